@@ -1,0 +1,206 @@
+/*
+ * mpsbnb_b200 — C ABI of the B200 (sm_100a) quantize / dequantize / fused dequant-matmul
+ * library.  Every function takes raw DEVICE pointers, sizes, and a CUDA stream
+ * (cudaStream_t passed as void*; NULL = legacy default stream), enqueues work on that
+ * stream WITHOUT synchronising, and returns a status code.  The library never allocates
+ * or frees tensor memory: outputs and workspaces are supplied by the caller.
+ *
+ * Each entry point names the function of the reference (mps-bitsandbytes v0.7.0) it
+ * stands in for: the Python function in mps_bitsandbytes/functional.py whose result it
+ * must reproduce, and — where one exists — the pybind11 binding of the reference's
+ * native extension, mps_bitsandbytes/csrc/mps_bitsandbytes.mm, that a maintainer would
+ * re-point at this symbol.
+ *
+ * Layouts are the reference's, unchanged:
+ *   packed 4-bit weights  uint8 [N, Kp/2], low nibble = even k, high nibble = odd k,
+ *                         Kp = K rounded up to a multiple of blocksize (functional.py:219-251)
+ *   absmax                fp32 [N, Kp/blocksize]; or, double-quantised, int8 of the same
+ *                         shape plus fp32 absmax2 [ceil(N*nb/256)] (functional.py:288-292)
+ */
+#ifndef MPSBNB_B200_H
+#define MPSBNB_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* status codes (0 = success, negative = failure) */
+#define MPSBNB_OK 0
+#define MPSBNB_ERR_INVALID_ARG (-1)   /* null pointer, bad enum, bad size                    */
+#define MPSBNB_ERR_UNSUPPORTED (-2)   /* shape / dtype combination this build cannot run     */
+#define MPSBNB_ERR_CUDA (-3)          /* a CUDA call failed: see mpsbnb_last_cuda_error()    */
+#define MPSBNB_ERR_WORKSPACE (-4)     /* workspace too small: see the *_workspace_bytes call */
+#define MPSBNB_ERR_TOO_LARGE (-5)     /* size beyond a documented fixed limit                */
+#define MPSBNB_ERR_NO_DEVICE (-6)     /* no sm_100 device is current                         */
+
+/* element types */
+#define MPSBNB_F16 0
+#define MPSBNB_BF16 1
+#define MPSBNB_F32 2
+/* 4-bit codebooks: functional.py:21-32 */
+#define MPSBNB_NF4 0
+#define MPSBNB_FP4 1
+
+const char *mpsbnb_status_string(int status);
+/* cudaError_t (as int) and text of the most recent failing CUDA call on this thread */
+int mpsbnb_last_cuda_error(void);
+const char *mpsbnb_last_cuda_error_string(void);
+/* ABI version: bumped on any signature change */
+int mpsbnb_abi_version(void);
+
+/* ---------------------------------------------------------------------------------------
+ * 4-bit blockwise quantise / dequantise
+ * ------------------------------------------------------------------------------------- */
+
+/* functional.py:163-303 quantize_4bit (2-D row-wise path :216-255; the flat path
+ * :257-286 is rows = 1, cols = numel).  Binding replaced: _C.quantize_nf4 /
+ * _C.quantize_fp4 (mps_bitsandbytes.mm:2738, 2746).
+ *   A          [rows, cols] row-major, a_dtype in {F16, BF16, F32}
+ *   absmax_in  optional fp32 [rows, nb]: use these block maxima instead of computing them
+ *   packed     out uint8 [rows, Kp/2]
+ *   absmax_out out fp32  [rows, nb]   (nb = Kp / blocksize); may be NULL if absmax_in given
+ * Bit-exact with the reference CPU path.  NaN inputs are not supported. */
+int mpsbnb_quantize_4bit(const void *A, int a_dtype, int64_t rows, int64_t cols, int blocksize,
+                         int quant_type, const float *absmax_in, uint8_t *packed,
+                         float *absmax_out, void *stream);
+
+/* functional.py:306-416 dequantize_4bit, with the double-quant expansion of :335-337
+ * folded in.  Binding replaced: _C.dequantize_nf4 / _C.dequantize_fp4
+ * (mps_bitsandbytes.mm:2739-2740, 2747-2748).
+ *   absmax   fp32 [rows, nb] when absmax2 == NULL, else int8 [rows, nb]
+ *   absmax2  NULL, or fp32 [ceil(rows*nb/256)] second-level maxima
+ *   out      [rows, cols] in out_dtype
+ * Bit-exact with the reference CPU path. */
+int mpsbnb_dequantize_4bit(const uint8_t *packed, const void *absmax, const float *absmax2,
+                           int64_t rows, int64_t cols, int blocksize, int quant_type, void *out,
+                           int out_dtype, void *stream);
+
+/* functional.py:469-539 quantize_blockwise (flat int8, used with blocksize 256 for the
+ * double quantisation of absmax, :291).  Binding replaced: _C.double_quant
+ * (mps_bitsandbytes.mm:2762) — but with the Python semantics (signed, 127/absmax).
+ *   A [n] a_dtype; absmax_in optional fp32 [nblk]; q out int8 [n]; absmax_out fp32 [nblk] */
+int mpsbnb_quantize_blockwise(const void *A, int a_dtype, int64_t n, int blocksize,
+                              const float *absmax_in, int8_t *q, float *absmax_out, void *stream);
+
+/* functional.py:542-600 dequantize_blockwise: out[i] = float(q[i]) * (absmax[i/bs] / 127). */
+int mpsbnb_dequantize_blockwise(const int8_t *q, const float *absmax, int64_t n, int blocksize,
+                                void *out, int out_dtype, void *stream);
+
+/* ---------------------------------------------------------------------------------------
+ * 4-bit fused dequantise-matmul:  y[M,N] = x[M,K] . W[N,K]^T (+ bias)
+ * functional.py:680-773 matmul_4bit / matmul_nf4 / matmul_fp4.
+ * Bindings replaced: _C.matmul_nf4 / _C.matmul_fp4 (mps_bitsandbytes.mm:2741-2743,
+ * 2749-2751; host wrappers :1956-2032, :2099-2151).
+ * x, bias in x_dtype (F16 or BF16); y in y_dtype; fp32 accumulation.
+ * ------------------------------------------------------------------------------------- */
+
+/* Decode shapes (M <= mpsbnb_gemv_4bit_max_m()): weights streamed once from HBM.
+ * Needs blocksize 64 (any K; Kp/2 bytes per row).  No workspace. */
+int mpsbnb_gemv_4bit_max_m(void);
+int mpsbnb_gemv_4bit(const void *x, int x_dtype, int64_t M, const uint8_t *packed,
+                     const void *absmax, const float *absmax2, int64_t N, int64_t K,
+                     int blocksize, int quant_type, const void *bias, void *y, int y_dtype,
+                     void *stream);
+
+/* Layer boundary of the synthetic decoder-layer stack used by the decode benchmark:
+ *   h[m, j] = alpha * (o[m, j] + d[m, j])  for j < H,   e[m, j] = h[m, j mod H]  for j < F
+ * (h: next layer's input; e: F-wide input of its down projection; e may be NULL).
+ * No reference counterpart: the reference ships no model, only the linear layers. */
+int mpsbnb_stack_boundary(const void *o, const void *d, int dtype, float alpha, int64_t M, int64_t H,
+                          int64_t F, void *h, void *e, void *stream);
+
+/* Multi-GPU form of the boundary: G[r][m][c] holds the all-gathered per-rank shards of the
+ * new h (c < H / nranks); writes h[m, r*H/nranks + c] = G[r][m][c] and e as above.
+ * No reference counterpart (the reference is single-device). */
+int mpsbnb_stack_expand(const void *G, int dtype, int64_t nranks, int64_t M, int64_t H, int64_t F,
+                        void *h, void *e, void *stream);
+
+/* Any M: dequantise W into the caller's workspace in x_dtype, then a tcgen05 tensor-core
+ * GEMM.  workspace must hold mpsbnb_gemm_4bit_workspace_bytes(...) bytes, 256-B aligned. */
+size_t mpsbnb_gemm_4bit_workspace_bytes(int64_t M, int64_t N, int64_t K, int blocksize);
+int mpsbnb_gemm_4bit(const void *x, int x_dtype, int64_t M, const uint8_t *packed,
+                     const void *absmax, const float *absmax2, int64_t N, int64_t K,
+                     int blocksize, int quant_type, const void *bias, void *y, int y_dtype,
+                     void *workspace, size_t workspace_bytes, void *stream);
+
+/* Dense tensor-core GEMM y[M,N] = a[M,K] . b[N,K]^T (+ bias), both operands K-major in
+ * ab_dtype (F16/BF16) with leading dimensions lda / ldb in elements (multiples of 8, bases
+ * 16-byte aligned: TMA row pitches), fp32 accumulation in tensor memory.  Building block of
+ * the prefill paths above and below; stands for torch.nn.functional.linear at
+ * functional.py:767, 806, 944.  Optional epilogue: y = acc * row_scale[m] * col_scale[n] + bias[n]
+ * (bias in ab_dtype).  K must be > 0. */
+int mpsbnb_gemm_f16(const void *a, int64_t lda, const void *b, int64_t ldb, int ab_dtype, int64_t M,
+                    int64_t N, int64_t K, const float *row_scale, const float *col_scale,
+                    const void *bias, void *y, int y_dtype, void *stream);
+
+/* Device-side status word of the current device: 0, or the code of the bounded wait that
+ * ran out inside a kernel (kernels never trap or spin forever; they record and return).
+ * Synchronises the device.  reset != 0 clears the word.  No reference counterpart: the
+ * reference reports Metal pipeline failures as exceptions (mps_bitsandbytes.mm:1739-1771). */
+int mpsbnb_device_status(int *status_out, int reset);
+
+/* ---------------------------------------------------------------------------------------
+ * INT8 row-wise, col+row, LLM.int8 statistics
+ * ------------------------------------------------------------------------------------- */
+
+/* functional.py:607-625 quantize_rowwise: q int8 [rows, cols], scales fp32 [rows] = row absmax. */
+int mpsbnb_quantize_rowwise(const void *x, int x_dtype, int64_t rows, int64_t cols, int8_t *q,
+                            float *scales, void *stream);
+/* functional.py:628-636 dequantize_rowwise: out = float(q) * (scales[row] / 127). */
+int mpsbnb_dequantize_rowwise(const int8_t *q, const float *scales, int64_t rows, int64_t cols,
+                              void *out, int out_dtype, void *stream);
+/* functional.py:814-863 double_quant: row- and column-quantised int8 copies with their
+ * statistics.  row_stats_in / col_stats_in optional (else computed and written to *_out). */
+int mpsbnb_double_quant(const void *A, int a_dtype, int64_t rows, int64_t cols,
+                        const float *row_stats_in, const float *col_stats_in, int8_t *out_row,
+                        int8_t *out_col, float *row_stats_out, float *col_stats_out, void *stream);
+/* functional.py:896-924 quantize_colrow: q = round(W * 127 / sqrt(r[n] c[k])). */
+int mpsbnb_quantize_colrow(const void *W, int w_dtype, int64_t rows, int64_t cols, int8_t *q,
+                           float *row_absmax, float *col_absmax, void *stream);
+/* functional.py:927-932 dequantize_colrow. */
+int mpsbnb_dequantize_colrow(const int8_t *q, const float *row_scales, const float *col_scales,
+                             int64_t rows, int64_t cols, void *out, int out_dtype, void *stream);
+
+/* functional.py:788-793 matmul_int8; binding replaced: _C.matmul_int8
+ * (mps_bitsandbytes.mm:2730-2732, kernel int8_matmul_dequant :155-196).
+ *   A int8 [M,K] with a_scales [M]; B int8 [K,N] (N contiguous) with b_scales [N];
+ *   y [M,N] = sum_k A B * a_scales[m] * b_scales[n] / 127^2, in y_dtype.
+ * workspace: mpsbnb_matmul_int8_workspace_bytes(M,N,K) bytes. */
+size_t mpsbnb_matmul_int8_workspace_bytes(int64_t M, int64_t N, int64_t K);
+int mpsbnb_matmul_int8(const int8_t *A, const int8_t *B, const float *a_scales,
+                       const float *b_scales, int64_t M, int64_t N, int64_t K, void *y,
+                       int y_dtype, void *workspace, size_t workspace_bytes, void *stream);
+
+/* functional.py:935-945 matmul_colrow and nn/linear8bit.py:91-102 (W8A16 with col_scales
+ * == NULL: plain row-wise weights); binding replaced: _C.linear_int8
+ * (mps_bitsandbytes.mm:2733-2735).  x [M,K] x_dtype, W int8 [N,K]. */
+size_t mpsbnb_linear_int8_workspace_bytes(int64_t M, int64_t N, int64_t K);
+int mpsbnb_linear_int8(const void *x, int x_dtype, int64_t M, const int8_t *W,
+                       const float *row_scales, const float *col_scales, int64_t N, int64_t K,
+                       const void *bias, void *y, int y_dtype, void *workspace,
+                       size_t workspace_bytes, void *stream);
+
+/* ---------------------------------------------------------------------------------------
+ * FP8 E4M3 (row-scaled)
+ * ------------------------------------------------------------------------------------- */
+
+/* functional.py:643-663 -> :1086-1163; binding replaced: _C.quantize_fp8_e4m3
+ * (mps_bitsandbytes.mm:2754), with the Python encoder's rounding (not the Metal one). */
+int mpsbnb_quantize_fp8_e4m3(const void *x, int x_dtype, int64_t rows, int64_t cols,
+                             uint8_t *codes, float *scales, void *stream);
+/* functional.py:666-673 -> :1166-1216; binding replaced: _C.dequantize_fp8_e4m3 (:2755-2756). */
+int mpsbnb_dequantize_fp8_e4m3(const uint8_t *codes, const float *scales, int64_t rows,
+                               int64_t cols, void *out, int out_dtype, void *stream);
+/* functional.py:796-807 matmul_fp8_e4m3; binding replaced: _C.matmul_fp8_e4m3 (:2757-2759). */
+size_t mpsbnb_linear_fp8_workspace_bytes(int64_t M, int64_t N, int64_t K);
+int mpsbnb_linear_fp8_e4m3(const void *x, int x_dtype, int64_t M, const uint8_t *codes,
+                           const float *scales, int64_t N, int64_t K, const void *bias, void *y,
+                           int y_dtype, void *workspace, size_t workspace_bytes, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MPSBNB_B200_H */

@@ -1,0 +1,20 @@
+// Internal (non-ABI) entry points shared between translation units.
+#pragma once
+#include "common.cuh"
+
+namespace mpsbnb {
+
+int dequantize_4bit_ld(const uint8_t *packed, const void *absmax, const float *absmax2, int64_t rows, int64_t cols,
+                       int blocksize, int quant_type, void *out, int64_t ld, int out_dtype, cudaStream_t st);
+int dequantize_i8_ld(const int8_t *q, int64_t rows, int64_t cols, const float *row_s, const float *col_s, void *out,
+                     int64_t ld, int out_dtype, cudaStream_t st);
+int dequantize_i8_transposed_ld(const int8_t *B, const float *col_s, int64_t K, int64_t N, void *out, int64_t ld,
+                                int out_dtype, cudaStream_t st);
+int dequantize_fp8_ld(const uint8_t *codes, const float *scales, int64_t rows, int64_t cols, void *out, int64_t ld,
+                      int out_dtype, cudaStream_t st);
+int copy_rows_16bit_ld(const void *src, int64_t rows, int64_t cols, void *dst, int64_t ld, cudaStream_t st);
+int gemm_16bit(const void *a, int64_t lda, const void *b, int64_t ldb, int ab_dtype, int64_t M, int64_t N, int64_t K,
+               const float *row_scale, const float *col_scale, const void *bias, int bias_dtype, void *y, int64_t ldy,
+               int y_dtype, cudaStream_t st);
+
+}  // namespace mpsbnb

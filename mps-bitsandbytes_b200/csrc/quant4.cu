@@ -1,0 +1,427 @@
+// Blockwise 4-bit (NF4 / FP4) quantise + pack, dequantise, and the blockwise int8
+// quantiser used for double quantisation of absmax.  All results are bit-identical to the
+// reference's CPU path (mps_bitsandbytes/functional.py:163-600).
+//
+// Quantise, fast path (16-bit input, block size 32..256, K % 8 == 0): every thread owns 8
+// consecutive elements (one 128-bit load), the bs/8 threads of a block reduce |x| with
+// warp shuffles, and each thread emits 4 packed bytes (one 32-bit store).  The nearest
+// code is found with 4 comparisons against decision thresholds instead of the reference's
+// 16-way |v - code| search; the thresholds are the exact floats at which the rounded
+// 16-way search changes its answer (ties included), and v = x / absmax is produced by a
+// reciprocal, a multiply and two fused corrections.  Both shortcuts are proven equal to
+// the reference arithmetic for every (x, absmax) pair of fp16 and of bf16 by
+// oracle/oracle.c:o_prove_quantizer with block maxima in [1e-30, 1e30]; fp32 input and maxima
+// outside that range use IEEE division.
+#include "common.cuh"
+
+namespace mpsbnb {
+
+// Largest v for which code i (and not i+1) is the first minimiser of |v - code|:
+// derived by oracle/oracle.c:o_nf4_thresholds, checked by tests/test_thresholds.py.
+#define NF4_T0 -0x1.b239b2p-1f
+#define NF4_T1 -0x1.38a4e2p-1f
+#define NF4_T2 -0x1.d709p-2f
+#define NF4_T3 -0x1.5bd4eep-2f
+#define NF4_T4 -0x1.e079dap-3f
+#define NF4_T5 -0x1.1a7178p-3f
+#define NF4_T6 -0x1.74f0e2p-5f
+#define NF4_T7 0x1.45f5fep-5f
+#define NF4_T8 0x1.ec90c4p-4f
+#define NF4_T9 0x1.a0cfcp-3f
+#define NF4_T10 0x1.2b05a8p-2f
+#define NF4_T11 0x1.8ea7f2p-2f
+#define NF4_T12 0x1.00da06p-1f
+#define NF4_T13 0x1.491b5ep-1f
+#define NF4_T14 0x1.b913b2p-1f
+// FP4 works on |v|: magnitudes 0, 1/16, 1/8, 1/4, 3/8, 1/2, 3/4, 1; ties go to the smaller.
+#define FP4_T0 0x1p-5f
+#define FP4_T1 0x1.8p-4f
+#define FP4_T2 0x1.8p-3f
+#define FP4_T3 0x1.4p-2f
+#define FP4_T4 0x1.cp-2f
+#define FP4_T5 0x1.4p-1f
+#define FP4_T6 0x1.cp-1f
+
+__device__ __forceinline__ uint32_t nf4_code(float v) {
+    uint32_t idx = v > NF4_T7 ? 8u : 0u;
+    float t = idx ? NF4_T11 : NF4_T3;
+    idx |= v > t ? 4u : 0u;
+    t = (idx & 8u) ? ((idx & 4u) ? NF4_T13 : NF4_T9) : ((idx & 4u) ? NF4_T5 : NF4_T1);
+    idx |= v > t ? 2u : 0u;
+    const float ta = (idx & 2u) ? NF4_T2 : NF4_T0, tb = (idx & 2u) ? NF4_T6 : NF4_T4;
+    const float tc = (idx & 2u) ? NF4_T10 : NF4_T8, td = (idx & 2u) ? NF4_T14 : NF4_T12;
+    t = (idx & 8u) ? ((idx & 4u) ? td : tc) : ((idx & 4u) ? tb : ta);
+    idx |= v > t ? 1u : 0u;
+    return idx;
+}
+
+__device__ __forceinline__ uint32_t fp4_code(float v) {
+    const float a = fabsf(v);
+    uint32_t m = a > FP4_T3 ? 4u : 0u;
+    float t = m ? FP4_T5 : FP4_T1;
+    m |= a > t ? 2u : 0u;
+    t = (m & 4u) ? ((m & 2u) ? FP4_T6 : FP4_T4) : ((m & 2u) ? FP4_T2 : FP4_T0);
+    m |= a > t ? 1u : 0u;
+    // negative values take codes 9..15; code 0 (+0.0) beats code 8 (-0.0) on the tie
+    return (v < 0.0f && m != 0u) ? (m | 8u) : m;
+}
+
+template <int QT> __device__ __forceinline__ uint32_t code_of(float v) {
+    return QT == MPSBNB_NF4 ? nf4_code(v) : fp4_code(v);
+}
+
+// x / a rounded to nearest, a > 0.  EXACT16: x and a are fp16- or bf16-representable and
+// 1e-30 <= a <= 1e30, where the 4-operation form is proven equal to IEEE division for
+// the purpose of code selection.
+template <bool EXACT16> __device__ __forceinline__ float block_div(float x, float a, float r) {
+    if (EXACT16) {
+        const float q = __fmul_rn(x, r);
+        return __fmaf_rn(__fmaf_rn(-q, a, x), r, q);
+    }
+    return __fdiv_rn(x, a);
+}
+
+// ------------------------------------------------------------------------------------------
+// Fast quantiser: 8 elements per thread, LPB = blocksize / 8 lanes per block.
+// ------------------------------------------------------------------------------------------
+template <typename T, int QT, int LPB>
+__global__ void __launch_bounds__(256)
+quantize4_fast_kernel(const T *__restrict__ A, int64_t rows, int64_t cols, int64_t chunks_per_row,
+                      const float *__restrict__ absmax_in, uint8_t *__restrict__ packed,
+                      float *__restrict__ absmax_out) {
+    static_assert(sizeof(T) == 2, "fast path takes 16-bit input");
+    const int64_t total = rows * chunks_per_row;           // multiple of LPB
+    const int64_t nwarp_iters = (total + 31) / 32;
+    const int lane = threadIdx.x & 31;
+    const int64_t warp0 = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int64_t nwarps = (int64_t)gridDim.x * (blockDim.x >> 5);
+    for (int64_t wi = warp0; wi < nwarp_iters; wi += nwarps) {
+        const int64_t c = wi * 32 + lane;
+        const bool live = c < total;
+        const int64_t row = live ? c / chunks_per_row : 0;
+        const int64_t kc = live ? c - row * chunks_per_row : 0;
+        const int64_t k0 = kc * 8;
+        uint4 raw = make_uint4(0u, 0u, 0u, 0u);            // zero padding beyond K
+        if (live && k0 < cols) raw = __ldg(reinterpret_cast<const uint4 *>(A + row * cols + k0));
+        float x[8];
+        {
+            const T *h = reinterpret_cast<const T *>(&raw);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) x[j] = to_f32<T>(h[j]);
+        }
+        const int64_t blk = row * (chunks_per_row / LPB) + kc / LPB;
+        float a;
+        if (absmax_in != nullptr) {
+            a = live ? absmax_in[blk] : 1.0f;
+        } else {
+            a = 0.0f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) a = fmaxf(a, fabsf(x[j]));
+#pragma unroll
+            for (int o = 1; o < LPB; o <<= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
+            a = fmaxf(a, 1e-8f);                           // clamp(min=1e-8)
+            if (live && (lane & (LPB - 1)) == 0) absmax_out[blk] = a;
+        }
+        uint32_t word = 0;
+        if (a >= 1e-30f && a <= 1e30f && absmax_in == nullptr) {   // range covered by the proof
+            const float r = __frcp_rn(a);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) word |= code_of<QT>(block_div<true>(x[j], a, r)) << (4 * j);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) word |= code_of<QT>(block_div<false>(x[j], a, 0.f)) << (4 * j);
+        }
+        if (live) reinterpret_cast<uint32_t *>(packed)[c] = word;   // byte j/2: low nibble = even k
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// General quantiser (any dtype, block size, K, alignment): block maxima with one warp per
+// block, then one thread per packed byte.
+// ------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void absmax_blocks_kernel(const T *__restrict__ A, int64_t rows, int64_t cols, int64_t bs,
+                                     int64_t nb, float *__restrict__ absmax_out) {
+    const int lane = threadIdx.x & 31;
+    const int64_t nblk = rows * nb;
+    const int64_t warp0 = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    for (int64_t b = warp0; b < nblk; b += (int64_t)gridDim.x * (blockDim.x >> 5)) {
+        const int64_t row = b / nb, k0 = (b - row * nb) * bs;
+        float a = 0.0f;
+        for (int64_t j = lane; j < bs; j += 32) {
+            const int64_t k = k0 + j;
+            if (k < cols) a = fmaxf(a, fabsf(to_f32<T>(A[row * cols + k])));
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
+        if (lane == 0) absmax_out[b] = fmaxf(a, 1e-8f);
+    }
+}
+
+template <typename T, int QT>
+__global__ void quantize4_bytes_kernel(const T *__restrict__ A, int64_t rows, int64_t cols, int64_t bs,
+                                       int64_t Kp, const float *__restrict__ absmax,
+                                       uint8_t *__restrict__ packed) {
+    const int64_t half = Kp / 2, total = rows * half, nb = Kp / bs;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t row = i / half, j = i - row * half;
+        uint32_t byte = 0;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int64_t k = 2 * j + h;
+            const float x = k < cols ? to_f32<T>(A[row * cols + k]) : 0.0f;
+            const float a = absmax[row * nb + k / bs];
+            byte |= code_of<QT>(__fdiv_rn(x, a)) << (4 * h);
+        }
+        packed[i] = (uint8_t)byte;
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// Dequantise.  absmax of block i: fp32 absmax[i], or float(q[i]) * (absmax2[i/256] / 127)
+// (mps_bitsandbytes/functional.py:592-593: divide first, then multiply).
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ float block_absmax(const void *absmax, const float *absmax2, int64_t i) {
+    if (absmax2 == nullptr) return __ldg(reinterpret_cast<const float *>(absmax) + i);
+    const float q = (float)__ldg(reinterpret_cast<const int8_t *>(absmax) + i);
+    return __fmul_rn(q, __fdiv_rn(__ldg(absmax2 + (i >> 8)), 127.0f));
+}
+
+// 16 elements (8 packed bytes) per thread; needs cols % 16 == 0 and blocksize >= 16.
+template <typename T, int QT>
+__global__ void __launch_bounds__(256)
+dequantize4_fast_kernel(const uint8_t *__restrict__ packed, const void *__restrict__ absmax,
+                        const float *__restrict__ absmax2, int64_t rows, int64_t cols, int64_t Kp,
+                        int bs_shift, T *__restrict__ out, int64_t ld) {
+    __shared__ float lut[16];
+    if (threadIdx.x < 16) lut[threadIdx.x] = kCode[QT][threadIdx.x];
+    __syncthreads();
+    const int64_t per_row = cols / 16, total = rows * per_row, nb = Kp >> bs_shift;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t row = i / per_row, k0 = (i - row * per_row) * 16;
+        const uint2 raw = __ldg(reinterpret_cast<const uint2 *>(packed + row * (Kp / 2) + k0 / 2));
+        const float a = block_absmax(absmax, absmax2, row * nb + (k0 >> bs_shift));
+        T vals[16];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const uint32_t w = j < 4 ? raw.x : raw.y;
+            const uint32_t byte = (w >> (8 * (j & 3))) & 0xFFu;
+            vals[2 * j] = from_f32<T>(__fmul_rn(lut[byte & 15u], a));
+            vals[2 * j + 1] = from_f32<T>(__fmul_rn(lut[byte >> 4], a));
+        }
+        T *dst = out + row * ld + k0;
+        if (sizeof(T) == 2) {
+            reinterpret_cast<uint4 *>(dst)[0] = reinterpret_cast<const uint4 *>(vals)[0];
+            reinterpret_cast<uint4 *>(dst)[1] = reinterpret_cast<const uint4 *>(vals)[1];
+        } else {
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+                reinterpret_cast<uint4 *>(dst)[q] = reinterpret_cast<const uint4 *>(vals)[q];
+        }
+    }
+}
+
+template <typename T, int QT>
+__global__ void dequantize4_elem_kernel(const uint8_t *__restrict__ packed, const void *__restrict__ absmax,
+                                        const float *__restrict__ absmax2, int64_t rows, int64_t cols,
+                                        int64_t Kp, int64_t bs, T *__restrict__ out, int64_t ld) {
+    const int64_t total = rows * cols, nb = Kp / bs;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t row = i / cols, k = i - row * cols;
+        const uint32_t byte = packed[row * (Kp / 2) + k / 2];
+        const uint32_t idx = (k & 1) ? (byte >> 4) : (byte & 15u);
+        out[row * ld + k] = from_f32<T>(__fmul_rn(kCode[QT][idx], block_absmax(absmax, absmax2, row * nb + k / bs)));
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// Blockwise int8 (mps_bitsandbytes/functional.py:469-600).  One CTA per block of `bs`
+// values.  scale = 127.0 / absmax is evaluated as reciprocal * 127 — torch computes
+// scalar / tensor as tensor.reciprocal() * scalar — which decides round-half-even ties.
+// ------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256)
+quantize_blockwise_kernel(const T *__restrict__ A, int64_t n, int64_t bs, const float *__restrict__ absmax_in,
+                          int8_t *__restrict__ q, float *__restrict__ absmax_out) {
+    __shared__ float red[8];
+    __shared__ float s_scale;
+    const int64_t nblk = (n + bs - 1) / bs;
+    for (int64_t b = blockIdx.x; b < nblk; b += gridDim.x) {
+        const int64_t i0 = b * bs;
+        const int64_t len = min(bs, n - i0);
+        float a;
+        if (absmax_in != nullptr) {
+            a = absmax_in[b];
+        } else {
+            a = 0.0f;
+            for (int64_t j = threadIdx.x; j < len; j += blockDim.x) a = fmaxf(a, fabsf(to_f32<T>(A[i0 + j])));
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
+            if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = a;
+            __syncthreads();
+            a = red[0];
+            for (int w = 1; w < (int)(blockDim.x >> 5); ++w) a = fmaxf(a, red[w]);
+            a = fmaxf(a, 1e-8f);
+        }
+        if (threadIdx.x == 0) {
+            if (absmax_out != nullptr) absmax_out[b] = a;
+            s_scale = __fmul_rn(__frcp_rn(a), 127.0f);
+        }
+        __syncthreads();
+        const float scale = s_scale;
+        for (int64_t j = threadIdx.x; j < len; j += blockDim.x) {
+            float v = rintf(__fmul_rn(to_f32<T>(A[i0 + j]), scale));   // round half to even
+            v = fminf(fmaxf(v, -127.0f), 127.0f);
+            q[i0 + j] = (int8_t)(int)v;
+        }
+        __syncthreads();
+    }
+}
+
+template <typename T>
+__global__ void dequantize_blockwise_kernel(const int8_t *__restrict__ q, const float *__restrict__ absmax,
+                                            int64_t n, int64_t bs, T *__restrict__ out) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+         i += (int64_t)gridDim.x * blockDim.x)
+        out[i] = from_f32<T>(__fmul_rn((float)q[i], __fdiv_rn(__ldg(absmax + i / bs), 127.0f)));
+}
+
+static int grid_for(int64_t work_items, int threads, int per_sm) {
+    int64_t g = (work_items + threads - 1) / threads;
+    const int64_t cap = (int64_t)sm_count() * per_sm;
+    if (g > cap) g = cap;
+    if (g < 1) g = 1;
+    return (int)g;
+}
+
+static int shift_of(int64_t v) {
+    int s = 0;
+    while ((1ll << s) < v) ++s;
+    return s;
+}
+
+}  // namespace mpsbnb
+
+using namespace mpsbnb;
+
+extern "C" int mpsbnb_quantize_4bit(const void *A, int a_dtype, int64_t rows, int64_t cols, int blocksize,
+                                    int quant_type, const float *absmax_in, uint8_t *packed,
+                                    float *absmax_out, void *stream) {
+    if (!valid_dtype(a_dtype) || (quant_type != MPSBNB_NF4 && quant_type != MPSBNB_FP4)) return MPSBNB_ERR_INVALID_ARG;
+    if (rows < 0 || cols < 0 || !is_pow2(blocksize) || blocksize > 65536) return MPSBNB_ERR_INVALID_ARG;
+    if (rows == 0 || cols == 0) return MPSBNB_OK;
+    if (A == nullptr || packed == nullptr || (absmax_in == nullptr && absmax_out == nullptr)) return MPSBNB_ERR_INVALID_ARG;
+    cudaStream_t st = (cudaStream_t)stream;
+    const int64_t Kp = padded_k(cols, blocksize), nb = Kp / blocksize;
+    const bool fast = is_16bit(a_dtype) && blocksize >= 32 && blocksize <= 256 && (cols % 8) == 0 &&
+                      aligned16(A) && ((reinterpret_cast<uintptr_t>(packed) & 3) == 0);
+    if (fast) {
+        const int64_t cpr = Kp / 8, total = rows * cpr;
+        const int grid = grid_for((total + 31) / 32 * 32, 256, 16);
+#define LAUNCH_FAST(T, QT, LPB)                                                                     \
+    quantize4_fast_kernel<T, QT, LPB><<<grid, 256, 0, st>>>((const T *)A, rows, cols, cpr, absmax_in, \
+                                                             packed, absmax_out)
+#define LAUNCH_FAST_QT(T, LPB)                                                   \
+    do {                                                                         \
+        if (quant_type == MPSBNB_NF4) LAUNCH_FAST(T, MPSBNB_NF4, LPB);           \
+        else LAUNCH_FAST(T, MPSBNB_FP4, LPB);                                    \
+    } while (0)
+#define LAUNCH_FAST_T(LPB)                                                       \
+    do {                                                                         \
+        if (a_dtype == MPSBNB_F16) LAUNCH_FAST_QT(__half, LPB);                  \
+        else LAUNCH_FAST_QT(__nv_bfloat16, LPB);                                 \
+    } while (0)
+        switch (blocksize) {
+            case 32: LAUNCH_FAST_T(4); break;
+            case 64: LAUNCH_FAST_T(8); break;
+            case 128: LAUNCH_FAST_T(16); break;
+            default: LAUNCH_FAST_T(32); break;
+        }
+        return check_launch();
+    }
+    const float *am = absmax_in;
+    if (am == nullptr) {
+        const int grid = grid_for(rows * nb * 32, 256, 16);
+        MPSBNB_DISPATCH_DTYPE(a_dtype, T, (absmax_blocks_kernel<T><<<grid, 256, 0, st>>>(
+                                              (const T *)A, rows, cols, blocksize, nb, absmax_out)));
+        int rc = check_launch();
+        if (rc != MPSBNB_OK) return rc;
+        am = absmax_out;
+    }
+    const int grid = grid_for(rows * (Kp / 2), 256, 16);
+    if (quant_type == MPSBNB_NF4)
+        MPSBNB_DISPATCH_DTYPE(a_dtype, T, (quantize4_bytes_kernel<T, MPSBNB_NF4><<<grid, 256, 0, st>>>(
+                                              (const T *)A, rows, cols, blocksize, Kp, am, packed)));
+    else
+        MPSBNB_DISPATCH_DTYPE(a_dtype, T, (quantize4_bytes_kernel<T, MPSBNB_FP4><<<grid, 256, 0, st>>>(
+                                              (const T *)A, rows, cols, blocksize, Kp, am, packed)));
+    return check_launch();
+}
+
+namespace mpsbnb {
+// Dequantise into a matrix with leading dimension ld (elements), ld >= cols.
+int dequantize_4bit_ld(const uint8_t *packed, const void *absmax, const float *absmax2, int64_t rows, int64_t cols,
+                       int blocksize, int quant_type, void *out, int64_t ld, int out_dtype, cudaStream_t st) {
+    if (!valid_dtype(out_dtype) || (quant_type != MPSBNB_NF4 && quant_type != MPSBNB_FP4)) return MPSBNB_ERR_INVALID_ARG;
+    if (rows < 0 || cols < 0 || ld < cols || !is_pow2(blocksize) || blocksize > 65536) return MPSBNB_ERR_INVALID_ARG;
+    if (rows == 0 || cols == 0) return MPSBNB_OK;
+    if (packed == nullptr || absmax == nullptr || out == nullptr) return MPSBNB_ERR_INVALID_ARG;
+    const int64_t Kp = padded_k(cols, blocksize);
+    const bool fast = blocksize >= 16 && (cols % 16) == 0 && aligned16(out) && (ld * dtype_bytes(out_dtype)) % 16 == 0 &&
+                      ((reinterpret_cast<uintptr_t>(packed) & 7) == 0);
+    if (fast) {
+        const int grid = grid_for(rows * (cols / 16), 256, 16);
+        const int sh = shift_of(blocksize);
+        if (quant_type == MPSBNB_NF4)
+            MPSBNB_DISPATCH_DTYPE(out_dtype, T, (dequantize4_fast_kernel<T, MPSBNB_NF4><<<grid, 256, 0, st>>>(
+                                                    packed, absmax, absmax2, rows, cols, Kp, sh, (T *)out, ld)));
+        else
+            MPSBNB_DISPATCH_DTYPE(out_dtype, T, (dequantize4_fast_kernel<T, MPSBNB_FP4><<<grid, 256, 0, st>>>(
+                                                    packed, absmax, absmax2, rows, cols, Kp, sh, (T *)out, ld)));
+        return check_launch();
+    }
+    const int grid = grid_for(rows * cols, 256, 16);
+    if (quant_type == MPSBNB_NF4)
+        MPSBNB_DISPATCH_DTYPE(out_dtype, T, (dequantize4_elem_kernel<T, MPSBNB_NF4><<<grid, 256, 0, st>>>(
+                                                packed, absmax, absmax2, rows, cols, Kp, blocksize, (T *)out, ld)));
+    else
+        MPSBNB_DISPATCH_DTYPE(out_dtype, T, (dequantize4_elem_kernel<T, MPSBNB_FP4><<<grid, 256, 0, st>>>(
+                                                packed, absmax, absmax2, rows, cols, Kp, blocksize, (T *)out, ld)));
+    return check_launch();
+}
+}  // namespace mpsbnb
+
+extern "C" int mpsbnb_dequantize_4bit(const uint8_t *packed, const void *absmax, const float *absmax2,
+                                      int64_t rows, int64_t cols, int blocksize, int quant_type, void *out,
+                                      int out_dtype, void *stream) {
+    return dequantize_4bit_ld(packed, absmax, absmax2, rows, cols, blocksize, quant_type, out, cols, out_dtype,
+                              (cudaStream_t)stream);
+}
+
+extern "C" int mpsbnb_quantize_blockwise(const void *A, int a_dtype, int64_t n, int blocksize,
+                                         const float *absmax_in, int8_t *q, float *absmax_out, void *stream) {
+    if (!valid_dtype(a_dtype) || n < 0 || blocksize <= 0 || blocksize > 65536) return MPSBNB_ERR_INVALID_ARG;
+    if (n == 0) return MPSBNB_OK;
+    if (A == nullptr || q == nullptr || (absmax_in == nullptr && absmax_out == nullptr)) return MPSBNB_ERR_INVALID_ARG;
+    const int64_t nblk = (n + blocksize - 1) / blocksize;
+    int64_t grid = nblk;
+    const int64_t cap = (int64_t)sm_count() * 16;
+    if (grid > cap) grid = cap;
+    MPSBNB_DISPATCH_DTYPE(a_dtype, T, (quantize_blockwise_kernel<T><<<(int)grid, 256, 0, (cudaStream_t)stream>>>(
+                                          (const T *)A, n, blocksize, absmax_in, q, absmax_out)));
+    return check_launch();
+}
+
+extern "C" int mpsbnb_dequantize_blockwise(const int8_t *q, const float *absmax, int64_t n, int blocksize,
+                                           void *out, int out_dtype, void *stream) {
+    if (!valid_dtype(out_dtype) || n < 0 || blocksize <= 0) return MPSBNB_ERR_INVALID_ARG;
+    if (n == 0) return MPSBNB_OK;
+    if (q == nullptr || absmax == nullptr || out == nullptr) return MPSBNB_ERR_INVALID_ARG;
+    const int grid = grid_for(n, 256, 16);
+    MPSBNB_DISPATCH_DTYPE(out_dtype, T, (dequantize_blockwise_kernel<T><<<grid, 256, 0, (cudaStream_t)stream>>>(
+                                            q, absmax, n, blocksize, (T *)out)));
+    return check_launch();
+}

@@ -1,0 +1,207 @@
+"""Synthetic decoder-layer stacks of Linear4bit layers (Llama-2-7B and Llama-70B shaped), the
+workload of the decode / prefill benchmarks, single-GPU or N-sharded over the GPUs of one box.
+
+The reference ships linear layers, not a model, so the dataflow between them is defined
+here.  Layer l takes a replicated activation h [M, H]:
+
+    q, k, v, o, gate, up = W_* . h          (six projections, all reading h)
+    down                 = W_down . e       (e [M, F]: h tiled along features, e[m, j] = h[m, j mod H])
+    h_next               = alpha * (o + down)        alpha keeps activations at unit scale
+
+Every projection is column (N) sharded over the ranks: rank r owns rows [r N/g, (r+1) N/g) of
+each packed weight and of its absmax — pure slices of the reference layout.  The only exchange
+is an all-gather of the [M, H/g] shard of h_next at the layer boundary.  q, k, v, gate, up are
+outputs of the layer (they stay sharded).
+
+One ``step`` runs all layers; it is captured once into a CUDA graph and replayed.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+from dataclasses import dataclass
+from typing import List, Optional
+
+import torch
+
+from . import _native as N
+from .functional import QuantState, _expand_absmax, quantize_4bit
+
+
+@dataclass
+class StackConfig:
+    name: str
+    hidden: int
+    ffn: int
+    kv: int          # output width of the k / v projections (GQA)
+    layers: int
+
+    def projections(self):
+        """(name, out_features, in_features) of the seven linears of one layer."""
+        H, F, KV = self.hidden, self.ffn, self.kv
+        return [("q", H, H), ("k", KV, H), ("v", KV, H), ("o", H, H), ("gate", F, H), ("up", F, H), ("down", H, F)]
+
+    def params_per_layer(self) -> int:
+        return sum(n * k for _, n, k in self.projections())
+
+    def alpha(self) -> float:
+        # std of (o + down) for unit-variance h and weights ~ N(0, 0.02)
+        return 1.0 / math.sqrt(0.02 ** 2 * (self.hidden + self.ffn))
+
+
+LLAMA2_7B = StackConfig("llama2-7b", 4096, 11008, 4096, 32)
+LLAMA_70B = StackConfig("llama-70b", 8192, 28672, 1024, 80)
+
+
+def weight_bytes(cfg: StackConfig, double_quant: bool = True, layers: Optional[int] = None) -> int:
+    """Packed + absmax bytes of the stack: 0.5 B per weight + absmax (fp32 per 64, or int8 per 64
+    plus fp32 per 16384 when double-quantised)."""
+    L = cfg.layers if layers is None else layers
+    total = 0
+    for _, n, k in cfg.projections():
+        nb = n * (k // 64)
+        total += n * k // 2 + (nb + 4 * ((nb + 255) // 256) if double_quant else 4 * nb)
+    return total * L
+
+
+def algorithmic_bytes(cfg: StackConfig, M: int, double_quant: bool = True, layers: Optional[int] = None) -> int:
+    """Bytes one step must move: every weight byte and absmax once, plus x and y of each linear (fp16)."""
+    L = cfg.layers if layers is None else layers
+    act = sum(2 * M * (n + k) for _, n, k in cfg.projections())
+    return weight_bytes(cfg, double_quant, layers) + act * L
+
+
+class _Proj:
+    __slots__ = ("name", "n", "k", "packed", "absmax", "absmax2", "state")
+
+
+class LayerStack:
+    """N-sharded stack of 4-bit linears.  ``rank`` / ``world`` select the shard (world = 1: whole)."""
+
+    def __init__(self, cfg: StackConfig, device, quant_type: str = "nf4", double_quant: bool = True,
+                 layers: Optional[int] = None, rank: int = 0, world: int = 1, seed: int = 1000,
+                 dtype: torch.dtype = torch.float16, group=None):
+        self.cfg, self.device, self.dtype = cfg, torch.device(device), dtype
+        self.layers = cfg.layers if layers is None else layers
+        self.rank, self.world, self.group = rank, world, group
+        self.quant_type, self.double_quant = quant_type, double_quant
+        self.alpha = cfg.alpha()
+        if cfg.hidden % world or cfg.ffn % world or cfg.kv % world:
+            raise ValueError("layer widths must divide by the number of ranks")
+        self.proj: List[List[_Proj]] = []
+        gen = torch.Generator(device=self.device)
+        for l in range(self.layers):
+            row = []
+            for i, (name, n, k) in enumerate(cfg.projections()):
+                ns = n // world
+                if (ns * (k // 64)) % 256 and double_quant:
+                    raise ValueError("shard does not align with the 256-block groups of double quantisation")
+                # the whole weight is drawn from the (layer, projection) seed, N(0, 0.02), and this
+                # rank keeps its rows: the model is the same for every world size
+                gen.manual_seed(seed + 7 * l + i)
+                full = torch.randn(n, k, device=self.device, generator=gen, dtype=torch.float32)
+                w = (full[rank * ns:(rank + 1) * ns] * 0.02).to(dtype)
+                del full
+                packed, st = quantize_4bit(w, blocksize=64, compress_statistics=double_quant, quant_type=quant_type)
+                del w
+                pr = _Proj()
+                pr.name, pr.n, pr.k, pr.packed, pr.state = name, ns, k, packed, st
+                pr.absmax, pr.absmax2 = _expand_absmax(st.absmax, st.state2)
+                row.append(pr)
+            self.proj.append(row)
+        self._graph = None
+        self._M = None
+
+    # ------------------------------------------------------------------ buffers
+    def _alloc(self, M: int):
+        cfg, dev, dt, g = self.cfg, self.device, self.dtype, self.world
+        self.h = torch.zeros(M, cfg.hidden, dtype=dt, device=dev)
+        self.e = torch.zeros(M, cfg.ffn, dtype=dt, device=dev)
+        self.out = {name: torch.zeros(M, n // g, dtype=dt, device=dev) for name, n, _ in cfg.projections()}
+        self.h_shard = torch.zeros(M, cfg.hidden // g, dtype=dt, device=dev)
+        self.gathered = torch.zeros(g, M, cfg.hidden // g, dtype=dt, device=dev) if g > 1 else None
+        self._M = M
+
+    def _gemv(self, pr: _Proj, x: torch.Tensor, y: torch.Tensor, M: int):
+        lib = N.lib()
+        if M <= lib.mpsbnb_gemv_4bit_max_m():
+            N.check(lib.mpsbnb_gemv_4bit(N.ptr(x), N.dt(self.dtype), N.i64(M), N.ptr(pr.packed), N.ptr(pr.absmax),
+                                         N.ptr(pr.absmax2), N.i64(pr.n), N.i64(pr.k), C.c_int(64),
+                                         C.c_int(N.qt(self.quant_type)), None, N.ptr(y), N.dt(self.dtype), N.stream()),
+                    "gemv_4bit")
+        else:
+            N.check(lib.mpsbnb_gemm_4bit(N.ptr(x), N.dt(self.dtype), N.i64(M), N.ptr(pr.packed), N.ptr(pr.absmax),
+                                         N.ptr(pr.absmax2), N.i64(pr.n), N.i64(pr.k), C.c_int(64),
+                                         C.c_int(N.qt(self.quant_type)), None, N.ptr(y), N.dt(self.dtype),
+                                         N.ptr(self._ws), C.c_size_t(self._ws.numel()), N.stream()), "gemm_4bit")
+
+    def _run_layers(self, M: int):
+        """Enqueue one step (all layers) on the current stream."""
+        cfg, lib, g = self.cfg, N.lib(), self.world
+        for l in range(self.layers):
+            for pr in self.proj[l]:
+                self._gemv(pr, self.e if pr.name == "down" else self.h, self.out[pr.name], M)
+            if g == 1:
+                N.check(lib.mpsbnb_stack_boundary(N.ptr(self.out["o"]), N.ptr(self.out["down"]), N.dt(self.dtype),
+                                                  C.c_float(self.alpha), N.i64(M), N.i64(cfg.hidden), N.i64(cfg.ffn),
+                                                  N.ptr(self.h), N.ptr(self.e), N.stream()), "stack_boundary")
+            else:
+                hs = cfg.hidden // g
+                N.check(lib.mpsbnb_stack_boundary(N.ptr(self.out["o"]), N.ptr(self.out["down"]), N.dt(self.dtype),
+                                                  C.c_float(self.alpha), N.i64(M), N.i64(hs), N.i64(hs),
+                                                  N.ptr(self.h_shard), None, N.stream()), "stack_boundary")
+                torch.distributed.all_gather_into_tensor(self.gathered, self.h_shard, group=self.group)
+                N.check(lib.mpsbnb_stack_expand(N.ptr(self.gathered), N.dt(self.dtype), N.i64(g), N.i64(M),
+                                                N.i64(cfg.hidden), N.i64(cfg.ffn), N.ptr(self.h), N.ptr(self.e),
+                                                N.stream()), "stack_expand")
+
+    # ------------------------------------------------------------------ public
+    def prepare(self, M: int, use_graph: bool = True):
+        """Allocate activations for batch M, and capture the step into a CUDA graph."""
+        with torch.cuda.device(self.device):
+            self._alloc(M)
+            lib = N.lib()
+            if M > lib.mpsbnb_gemv_4bit_max_m():
+                big = max(lib.mpsbnb_gemm_4bit_workspace_bytes(N.i64(M), N.i64(p.n), N.i64(p.k), C.c_int(64))
+                          for p in self.proj[0])
+                self._ws = torch.empty(big, dtype=torch.uint8, device=self.device)
+            self.x_in = torch.zeros(M, self.cfg.hidden, dtype=self.dtype, device=self.device)
+            self._graph = None
+            if use_graph:
+                s = torch.cuda.Stream(device=self.device)
+                s.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(s):
+                    self._load_input()
+                    self._run_layers(M)             # warm-up outside capture (function attributes, NCCL)
+                torch.cuda.current_stream().wait_stream(s)
+                torch.cuda.synchronize()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    self._load_input()
+                    self._run_layers(M)
+                self._graph = graph
+
+    def _load_input(self):
+        """h = x_in, e = tile(x_in): the stack's input stage (uses the expand kernel with one rank)."""
+        cfg = self.cfg
+        N.check(N.lib().mpsbnb_stack_expand(N.ptr(self.x_in), N.dt(self.dtype), N.i64(1), N.i64(self._M),
+                                            N.i64(cfg.hidden), N.i64(cfg.ffn), N.ptr(self.h), N.ptr(self.e),
+                                            N.stream()), "stack_expand")
+
+    def step(self, x: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """One pass of all layers.  ``x`` [M, H] (device) replaces the input; returns h of the last layer."""
+        if self._M is None:
+            raise RuntimeError("call prepare(M) first")
+        with torch.cuda.device(self.device):
+            if x is not None:
+                self.x_in.copy_(x, non_blocking=True)
+            if self._graph is not None:
+                self._graph.replay()
+            else:
+                self._load_input()
+                self._run_layers(self._M)
+        return self.h
+
+    def launches_per_step(self) -> int:
+        per_layer = 7 + (1 if self.world == 1 else 2)
+        return 1 + self.layers * per_layer
