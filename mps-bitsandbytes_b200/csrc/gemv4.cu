@@ -119,11 +119,20 @@ __global__ void __launch_bounds__(kWarps * 32, 2) gemv4_kernel(const Gemv4Params
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
 
-    // lane-replicated byte -> (code[lo nibble], code[hi nibble]) table
-    for (int i = tid; i < 256 * 32; i += kWarps * 32) {
-        const int byte = i >> 5, l = i & 31;
-        const uint32_t v = pack_pair<XT>(kCode[p.quant_type][byte & 15], kCode[p.quant_type][byte >> 4]);
-        *reinterpret_cast<uint32_t *>(smem + byte * 256 + l * 4) = v;
+    // lane-replicated byte -> (code[lo nibble], code[hi nibble]) table.  Warp w fills bytes
+    // 32 w .. 32 w + 31: lane l computes the pair of byte 32 w + l once, and in round j every lane
+    // stores byte (32 w + j)'s pair into its own replica (consecutive lanes, consecutive banks).
+    {
+        const float my_code = kCode[p.quant_type][lane & 15];
+        const int byte = warp * 32 + lane;
+        const float lo = __shfl_sync(0xffffffffu, my_code, byte & 15);
+        const float hi = __shfl_sync(0xffffffffu, my_code, byte >> 4);
+        const uint32_t mine = pack_pair<XT>(lo, hi);
+#pragma unroll 8
+        for (int j = 0; j < 32; ++j) {
+            const uint32_t v = __shfl_sync(0xffffffffu, mine, j);
+            *reinterpret_cast<uint32_t *>(smem + (warp * 32 + j) * 256 + lane * 4) = v;
+        }
     }
     __syncthreads();
 

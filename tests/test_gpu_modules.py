@@ -66,5 +66,9 @@ def test_linear8bit_cache_and_fp8_dequantize(golden):
     assert l8.weight_int8.dtype == torch.int8 and l8.weight_scales.dtype == torch.float32
     f8 = bnb.LinearFP8.from_linear(lin)
     assert tuple(f8.dequantize().shape) == (48, 128)
-    err = (f8.dequantize().float() - lin.weight.float()).abs().max() / lin.weight.float().abs().max()
-    assert err < 0.07
+    # the reference's encoder maps everything in (240, 448] — the row maximum included — to 240,
+    # so the check is parity with the oracle, not closeness to the original weight
+    from oracle import oracle_np as O
+    c8, s8 = O.quantize_fp8_e4m3(g["mod_w"])
+    assert np.array_equal(to_np(f8.weight_fp8), c8) and np.array_equal(to_np(f8.weight_scales), s8)
+    assert np.array_equal(to_np(f8.dequantize()), O.dequantize_fp8_e4m3(c8, s8, "float16"))
