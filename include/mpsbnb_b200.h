@@ -105,12 +105,53 @@ int mpsbnb_gemv_4bit(const void *x, int x_dtype, int64_t M, const uint8_t *packe
                      int blocksize, int quant_type, const void *bias, void *y, int y_dtype,
                      void *stream);
 
+/* Grouped decode GEMV: several 4-bit linears (block size 64, batch M <= 8) in ONE launch of
+ * a persistent kernel, e.g. the seven projections of a decoder layer.  Replaces a sequence
+ * of _C.matmul_nf4 / _C.matmul_fp4 calls (mps_bitsandbytes.mm:2741-2751), which the
+ * reference issues one Metal dispatch at a time.
+ *   x        [M, x_ld] activations; column k of the product reads x[m, k mod x_period]
+ *            (x_period = 0 means K: no wrap)
+ *   y / acc  results are stored to y [M, N] (y_dtype), or — when acc != NULL — atomically
+ *            added to the fp32 matrix acc [M, N] (several linears may share one acc; long
+ *            K is then split across CTAs).  The caller zeroes acc.
+ * A plan (device memory supplied by the caller, 256-byte aligned, size from
+ * mpsbnb_gemv_4bit_group_plan_bytes) is built once and run any number of times. */
+typedef struct mpsbnb_linear4_desc {
+    const void *x;
+    int64_t x_ld, x_period;
+    const uint8_t *packed;
+    const void *absmax;
+    const float *absmax2;
+    const void *bias;
+    void *y;
+    float *acc;
+    int64_t N, K;
+} mpsbnb_linear4_desc;
+
+typedef struct mpsbnb_group_plan {
+    void *dev;
+    int64_t units_offset;
+    int n_linears, n_units, M, x_dtype, quant_type, reserved;
+} mpsbnb_group_plan;
+
+size_t mpsbnb_gemv_4bit_group_plan_bytes(const mpsbnb_linear4_desc *descs, int n_linears);
+/* Builds the plan (synchronises the stream once: it uploads the tables). */
+int mpsbnb_gemv_4bit_group_plan(const mpsbnb_linear4_desc *descs, int n_linears, int64_t M, int x_dtype,
+                                int y_dtype, int quant_type, void *plan_dev, size_t plan_bytes,
+                                mpsbnb_group_plan *plan_out, void *stream);
+int mpsbnb_gemv_4bit_group_run(const mpsbnb_group_plan *plan, void *stream);
+
 /* Layer boundary of the synthetic decoder-layer stack used by the decode benchmark:
  *   h[m, j] = alpha * (o[m, j] + d[m, j])  for j < H,   e[m, j] = h[m, j mod H]  for j < F
  * (h: next layer's input; e: F-wide input of its down projection; e may be NULL).
  * No reference counterpart: the reference ships no model, only the linear layers. */
 int mpsbnb_stack_boundary(const void *o, const void *d, int dtype, float alpha, int64_t M, int64_t H,
                           int64_t F, void *h, void *e, void *stream);
+
+/* Boundary for the grouped path, where o and down were atomically accumulated into one fp32
+ * matrix: h[i] = alpha * acc[i] (i < n, rounded to dtype) and acc[i] = 0.
+ * No reference counterpart. */
+int mpsbnb_stack_boundary_acc(float *acc, float alpha, int64_t n, void *h, int dtype, void *stream);
 
 /* Multi-GPU form of the boundary: G[r][m][c] holds the all-gathered per-rank shards of the
  * new h (c < H / nranks); writes h[m, r*H/nranks + c] = G[r][m][c] and e as above.

@@ -22,6 +22,19 @@ _QT = {"nf4": NF4, "fp4": FP4}
 _lib = None
 
 
+class Linear4Desc(C.Structure):
+    """mpsbnb_linear4_desc of include/mpsbnb_b200.h."""
+    _fields_ = [("x", C.c_void_p), ("x_ld", C.c_int64), ("x_period", C.c_int64), ("packed", C.c_void_p),
+                ("absmax", C.c_void_p), ("absmax2", C.c_void_p), ("bias", C.c_void_p), ("y", C.c_void_p),
+                ("acc", C.c_void_p), ("N", C.c_int64), ("K", C.c_int64)]
+
+
+class GroupPlan(C.Structure):
+    """mpsbnb_group_plan of include/mpsbnb_b200.h."""
+    _fields_ = [("dev", C.c_void_p), ("units_offset", C.c_int64), ("n_linears", C.c_int), ("n_units", C.c_int),
+                ("M", C.c_int), ("x_dtype", C.c_int), ("quant_type", C.c_int), ("reserved", C.c_int)]
+
+
 class NativeLibraryError(RuntimeError):
     pass
 
@@ -37,7 +50,7 @@ def lib():
         l = C.CDLL(LIB_PATH)
         l.mpsbnb_status_string.restype = C.c_char_p
         l.mpsbnb_last_cuda_error_string.restype = C.c_char_p
-        for name in ("mpsbnb_gemm_4bit_workspace_bytes", "mpsbnb_matmul_int8_workspace_bytes",
+        for name in ("mpsbnb_gemv_4bit_group_plan_bytes", "mpsbnb_gemm_4bit_workspace_bytes", "mpsbnb_matmul_int8_workspace_bytes",
                      "mpsbnb_linear_int8_workspace_bytes", "mpsbnb_linear_fp8_workspace_bytes"):
             if hasattr(l, name):
                 getattr(l, name).restype = C.c_size_t

@@ -14,6 +14,7 @@
 // Every mbarrier wait is bounded: on time-out the role records a status word, raises a
 // CTA-wide abort flag and all roles fall through to the common exit, which frees TMEM.
 #include "common.cuh"
+#include "ops.cuh"
 #include "sm100.cuh"
 
 namespace mpsbnb {
@@ -23,7 +24,7 @@ using namespace sm100;
 constexpr int BM = 128, BK = 64, STAGES = 4;
 constexpr int GEMM_THREADS = 192;
 
-__device__ int g_device_status = 0;            // 0 = ok; set by a kernel whose bounded wait ran out
+static __device__ int g_device_status = 0;            // 0 = ok; set by a kernel whose bounded wait ran out
 
 struct GemmEpilogue {
     const float *row_scale;                    // nullptr or [M]
@@ -301,6 +302,10 @@ extern "C" int mpsbnb_device_status(int *status_out, int reset) {
         const int zero = 0;
         MPSBNB_CUDA_TRY(cudaMemcpyToSymbol(g_device_status, &zero, sizeof(int)));
     }
+    int other = 0;
+    const int rc = stream_status_fetch(&other, reset != 0);
+    if (rc != MPSBNB_OK) return rc;
+    if (*status_out == 0) *status_out = other;
     return MPSBNB_OK;
 }
 

@@ -25,6 +25,7 @@
 // tcgen05.mma must sit in shared memory, which would add a store and a load per weight to
 // the one resource (shared-memory bandwidth) that is already the tightest.
 #include "common.cuh"
+#include "ops.cuh"
 
 namespace mpsbnb {
 
@@ -320,9 +321,32 @@ __global__ void stack_expand_kernel(const T *__restrict__ G, int g, int M, int H
     }
 }
 
+// h[i] = alpha * acc[i] (rounded to T), then acc[i] = 0: closes a layer whose o and down
+// projections were accumulated into one fp32 matrix, and re-arms the accumulator.
+template <typename T>
+__global__ void stack_boundary_acc_kernel(float *__restrict__ acc, float alpha, int64_t n, T *__restrict__ h) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        h[i] = from_f32<T>(alpha * acc[i]);
+        acc[i] = 0.0f;
+    }
+}
+
 }  // namespace mpsbnb
 
 using namespace mpsbnb;
+
+extern "C" int mpsbnb_stack_boundary_acc(float *acc, float alpha, int64_t n, void *h, int dtype, void *stream) {
+    if (!is_16bit(dtype) || n < 0) return MPSBNB_ERR_INVALID_ARG;
+    if (n == 0) return MPSBNB_OK;
+    if (acc == nullptr || h == nullptr) return MPSBNB_ERR_INVALID_ARG;
+    int64_t grid = (n + 255) / 256;
+    if (grid > sm_count() * 8) grid = sm_count() * 8;
+    if (dtype == MPSBNB_F16)
+        stack_boundary_acc_kernel<__half><<<(int)grid, 256, 0, (cudaStream_t)stream>>>(acc, alpha, n, (__half *)h);
+    else
+        stack_boundary_acc_kernel<__nv_bfloat16><<<(int)grid, 256, 0, (cudaStream_t)stream>>>(acc, alpha, n, (__nv_bfloat16 *)h);
+    return check_launch();
+}
 
 extern "C" int mpsbnb_stack_expand(const void *G, int dtype, int64_t nranks, int64_t M, int64_t H, int64_t F, void *h,
                                    void *e, void *stream) {
@@ -380,5 +404,7 @@ extern "C" int mpsbnb_gemv_4bit(const void *x, int x_dtype, int64_t M, const uin
         p.K = 0;
     }
     cudaStream_t st = (cudaStream_t)stream;
+    if (M <= 8 && K > 0 && aligned16(packed))                  // TMA-fed streaming kernel
+        return gemv4_stream_single(x, x_dtype, M, packed, absmax, absmax2, N, K, quant_type, bias, y, y_dtype, st);
     return x_dtype == MPSBNB_F16 ? dispatch_gemv4<__half>(p, st) : dispatch_gemv4<__nv_bfloat16>(p, st);
 }

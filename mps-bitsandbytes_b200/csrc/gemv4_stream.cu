@@ -1,0 +1,750 @@
+// Streaming decode GEMV for 4-bit weights (block size 64), batch M <= 8, one or many linears
+// per launch:   y[m, n] = sum_k x[m, k] * code[W[n, k]] * absmax[n, k / 64]   (+ bias[n]).
+// Stands for mps_bitsandbytes/functional.py:680-773 on decode shapes (the reference's Metal
+// analogue is nf4_matmul_simd, mps_bitsandbytes.mm:440-560, launched once per linear).
+//
+// Bound: HBM.  Every packed byte crosses the memory system once.  One persistent CTA per SM
+// with 21 warps:
+//   warp 16  TMA producer.  Work is cut into units of 32 weight rows x a run of stages; a
+//            stage is 32 rows x 1024 k = 16 KB of packed bytes, fetched as four
+//            cp.async.bulk.tensor boxes (32 rows x 128 B, 128-byte swizzle) into a ring of
+//            shared-memory slots.  The ring keeps 100+ KB in flight per SM regardless of what the
+//            consumers are doing (register prefetch could not: it was the limiter before).
+//   warps 17-19  loaders, taking stages in turn.  For its stage a loader writes, into the same
+//            slot, the 32 x 16 block scales already expanded to fp32 (double-quantised absmax is
+//            int8 * absmax2 / 127) and the 1024 x values of each batch row, so consumers never
+//            touch global memory.  Three of them keep three stages' worth of loads in flight.
+//   warps 0-15  consumers.  Warp (rt, kg) owns row tile rt (16 rows) and blocks 2 kg, 2 kg + 1
+//            of every stage.  Per block: two 8-byte shared loads (rows g and g + 8 — the swizzle
+//            and a row permutation make them bank-conflict free), 16 table lookups that turn a
+//            packed byte into a pair of 16-bit codes (one byte-permute + one shared load each,
+//            table replicated per lane), 4 mma.sync.m16n8k16 with the weights as the M side,
+//            then one fp32 multiply-add per row with the block scale.
+//   warp 20  reducer.  At the end of a unit every consumer warp drops its partial sums into a
+//            double-buffered shared array and signals an mbarrier; the reducer adds the eight kg
+//            partials of each row and stores them (or atomically adds them to an fp32
+//            accumulator when K is split across units or several linears sum into one output).
+//            Consumers never wait for each other, and producers run ahead into the next unit, so
+//            the HBM stream does not pause at unit boundaries.
+// All waits are bounded (see sm100.cuh); a time-out sets the device status word.
+#include "common.cuh"
+#include "ops.cuh"
+#include "sm100.cuh"
+
+#include <stdlib.h>
+#include <string.h>
+
+namespace mpsbnb {
+
+using namespace sm100;
+
+constexpr int SG_CONSUMERS = 16;
+constexpr int SG_LOADERS = 3;
+constexpr int SG_THREADS = (SG_CONSUMERS + 1 + SG_LOADERS + 1) * 32;   // + TMA warp + reducer warp
+constexpr int SG_ROWS = 32;                              // weight rows per unit
+constexpr int SG_STAGE_BLOCKS = 16;                      // quantisation blocks (of 64 k) per stage
+constexpr int SG_W_BYTES = SG_ROWS * SG_STAGE_BLOCKS * 32;   // 16384 packed bytes per stage
+constexpr int SG_A_BYTES = SG_STAGE_BLOCKS * SG_ROWS * 4;    // 2048: fp32 scale [block][row]
+constexpr int SG_XPITCH = 2048 + 64;                     // bytes between batch rows of x in a slot
+constexpr int SG_RED_BYTES = SG_CONSUMERS * 8 * 20 * 4;  // [warp][m][16 rows + 4 pad] fp32
+constexpr int SG_MAX_SLOTS = 8;
+constexpr int SG_L2_AHEAD = 16;                         // stages pulled into L2 ahead of the ring
+constexpr int SG_MAX_M = 8;
+
+// status word of this translation unit (device code is not linked relocatably); read by
+// stream_status_fetch() on behalf of mpsbnb_device_status()
+static __device__ int g_stream_status = 0;
+
+struct StreamLinear {
+    CUtensorMap map;          // packed weights as [N][row_bytes] bytes; box 128 B x 32 rows, 128-byte swizzle
+    const void *x;            // activations [M, x_ld]; column index is taken modulo x_period
+    const void *absmax;       // fp32 [N, nb], or int8 [N, nb] when absmax2 != nullptr
+    const float *absmax2;     // fp32 [ceil(N nb / 256)] or nullptr
+    const void *bias;         // [N] in the activation dtype, or nullptr
+    void *y;                  // [M, N] in y_dtype; used when acc == nullptr
+    float *acc;               // fp32 [M, N] atomicAdd target, or nullptr
+    int64_t x_ld;
+    int N, K, nb, nbv;        // nb: blocks per row in the layout; nbv: blocks that hold real k
+    int x_period;             // x column = k mod x_period (x_period >= K: plain)
+    int y_dtype;
+    int x_vec_ok;             // 16-byte loads of x are legal
+    int x_bulk_ok;            // every stage's x columns are one 16-byte-aligned contiguous run: TMA bulk copies
+};
+
+struct StreamUnit { int lin, row0, s_begin, s_end; };
+
+struct StreamArgs {
+    const StreamLinear *lins; // device array, or nullptr: use `one`
+    const StreamUnit *units;  // device array, or nullptr: unit u = rows [32 u, 32 u + 32) x all stages of `one`
+    int nunits, M, quant_type, nslots, slot_bytes;
+    int debug;                // DEBUGVAR
+    uint32_t zero;            // always 0; known only at run time (orders the slot release after the loads)
+    StreamLinear one;
+};
+
+__device__ __forceinline__ void mma16816_f16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void mma16816_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+template <typename XT> __device__ __forceinline__ void mma_x(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1);
+template <> __device__ __forceinline__ void mma_x<__half>(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) { mma16816_f16(d, a0, a1, a2, a3, b0, b1); }
+template <> __device__ __forceinline__ void mma_x<__nv_bfloat16>(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) { mma16816_bf16(d, a0, a1, a2, a3, b0, b1); }
+
+template <typename XT> __device__ __forceinline__ uint32_t pair_bits(float lo, float hi);
+template <> __device__ __forceinline__ uint32_t pair_bits<__half>(float lo, float hi) { const __half2 h = __floats2half2_rn(lo, hi); return *reinterpret_cast<const uint32_t *>(&h); }
+template <> __device__ __forceinline__ uint32_t pair_bits<__nv_bfloat16>(float lo, float hi) { const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi); return *reinterpret_cast<const uint32_t *>(&h); }
+
+// ---- shared-memory access by 32-bit shared address (no generic-pointer arithmetic in the hot loop)
+template <int OFF> __device__ __forceinline__ uint2 lds64(uint32_t addr) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0, %1}, [%2+%3];" : "=r"(v.x), "=r"(v.y) : "r"(addr), "n"(OFF));
+    return v;
+}
+template <int OFF> __device__ __forceinline__ uint4 lds128(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4+%5];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr), "n"(OFF));
+    return v;
+}
+template <int OFF> __device__ __forceinline__ float lds_f32(uint32_t addr) {
+    float v;
+    asm volatile("ld.shared.f32 %0, [%1+%2];" : "=f"(v) : "r"(addr), "n"(OFF));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ void sts_f32(uint32_t addr, float v) { asm volatile("st.shared.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory"); }
+__device__ __forceinline__ void sts32(uint32_t addr, uint32_t v) { asm volatile("st.shared.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory"); }
+__device__ __forceinline__ void sts128(uint32_t addr, uint4 v) {
+    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+// d = a * b + c  (m16n8k16, fp32 accumulate)
+template <typename XT> __device__ __forceinline__ void mma_abc(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1, const float (&c)[4]);
+template <> __device__ __forceinline__ void mma_abc<__half>(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1, const float (&c)[4]) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
+                 : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(c[0]), "f"(c[1]), "f"(c[2]), "f"(c[3]));
+}
+template <> __device__ __forceinline__ void mma_abc<__nv_bfloat16>(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1, const float (&c)[4]) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
+                 : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(c[0]), "f"(c[1]), "f"(c[2]), "f"(c[3]));
+}
+
+// A consumer warp's work on one quantisation block (16 weight rows x 64 k) is written in PTX so
+// that the instruction stream is exactly what the design counts on.
+// fetch_block: 3 address adds and 6 shared loads bring the block's operands into registers —
+//   8 packed bytes of row g and of row g + 8, the two block scales, and 16 x values (the x
+//   registers stay zero in lanes that have no batch row).  After it the slot is no longer needed.
+__device__ __forceinline__ void fetch_block(uint32_t (&w)[4], float (&am)[2], uint32_t (&xr)[8], uint32_t sb,
+                                            uint32_t woff, uint32_t aoff, uint32_t xoff, uint32_t hasx) {
+    asm volatile(
+        "{\n\t"
+        ".reg .b32 aw, aa, ax;\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.u32 p, %18, 0;\n\t"
+        "add.u32 aw, %14, %15;\n\t"
+        "add.u32 aa, %14, %16;\n\t"
+        "add.u32 ax, %14, %17;\n\t"
+        "ld.shared.v2.u32 {%0, %1}, [aw];\n\t"
+        "ld.shared.v2.u32 {%2, %3}, [aw+1024];\n\t"
+        "@p ld.shared.v4.u32 {%6, %7, %8, %9}, [ax];\n\t"
+        "@p ld.shared.v4.u32 {%10, %11, %12, %13}, [ax+16];\n\t"
+        "ld.shared.f32 %4, [aa];\n\t"
+        "ld.shared.f32 %5, [aa+32];\n\t"
+        "}\n"
+        : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]), "=f"(am[0]), "=f"(am[1]), "+r"(xr[0]), "+r"(xr[1]),
+          "+r"(xr[2]), "+r"(xr[3]), "+r"(xr[4]), "+r"(xr[5]), "+r"(xr[6]), "+r"(xr[7])
+        : "r"(sb), "r"(woff), "r"(aoff), "r"(xoff), "r"(hasx)
+        : "memory");
+}
+
+// compute_block: 16 x (byte-permute, table load) turn the packed bytes into MMA A fragments
+//   (w[0], w[1]: row g; w[2], w[3]: row g + 8), 4 MMAs contract them with x, and 4 FMAs apply the
+//   two block scales.  lw is the lane word of the table address.
+#define MPSBNB_COMPUTE_ASM(TYPE)                                                                            \
+    asm volatile(                                                                                           \
+        "{\n\t"                                                                                             \
+        ".reg .b32 ad;\n\t"                                                                                 \
+        ".reg .b32 f<16>;\n\t"                                                                              \
+        ".reg .f32 t<4>, z;\n\t"                                                                            \
+        "mov.f32 z, 0f00000000;\n\t"                                                                        \
+        "prmt.b32 ad, %4, %18, 0x7604;\n\t ld.shared.u32 f0, [ad];\n\t"                                     \
+        "prmt.b32 ad, %6, %18, 0x7604;\n\t ld.shared.u32 f1, [ad];\n\t"                                     \
+        "prmt.b32 ad, %4, %18, 0x7614;\n\t ld.shared.u32 f2, [ad];\n\t"                                     \
+        "prmt.b32 ad, %6, %18, 0x7614;\n\t ld.shared.u32 f3, [ad];\n\t"                                     \
+        "prmt.b32 ad, %4, %18, 0x7624;\n\t ld.shared.u32 f4, [ad];\n\t"                                     \
+        "prmt.b32 ad, %6, %18, 0x7624;\n\t ld.shared.u32 f5, [ad];\n\t"                                     \
+        "prmt.b32 ad, %4, %18, 0x7634;\n\t ld.shared.u32 f6, [ad];\n\t"                                     \
+        "prmt.b32 ad, %6, %18, 0x7634;\n\t ld.shared.u32 f7, [ad];\n\t"                                     \
+        "prmt.b32 ad, %5, %18, 0x7604;\n\t ld.shared.u32 f8, [ad];\n\t"                                     \
+        "prmt.b32 ad, %7, %18, 0x7604;\n\t ld.shared.u32 f9, [ad];\n\t"                                     \
+        "prmt.b32 ad, %5, %18, 0x7614;\n\t ld.shared.u32 f10, [ad];\n\t"                                    \
+        "prmt.b32 ad, %7, %18, 0x7614;\n\t ld.shared.u32 f11, [ad];\n\t"                                    \
+        "prmt.b32 ad, %5, %18, 0x7624;\n\t ld.shared.u32 f12, [ad];\n\t"                                    \
+        "prmt.b32 ad, %7, %18, 0x7624;\n\t ld.shared.u32 f13, [ad];\n\t"                                    \
+        "prmt.b32 ad, %5, %18, 0x7634;\n\t ld.shared.u32 f14, [ad];\n\t"                                    \
+        "prmt.b32 ad, %7, %18, 0x7634;\n\t ld.shared.u32 f15, [ad];\n\t"                                    \
+        "mma.sync.aligned.m16n8k16.row.col.f32." TYPE "." TYPE ".f32 {t0,t1,t2,t3}, {f0,f1,f2,f3}, {%10,%11}, {z,z,z,z};\n\t"        \
+        "mma.sync.aligned.m16n8k16.row.col.f32." TYPE "." TYPE ".f32 {t0,t1,t2,t3}, {f4,f5,f6,f7}, {%12,%13}, {t0,t1,t2,t3};\n\t"    \
+        "mma.sync.aligned.m16n8k16.row.col.f32." TYPE "." TYPE ".f32 {t0,t1,t2,t3}, {f8,f9,f10,f11}, {%14,%15}, {t0,t1,t2,t3};\n\t"  \
+        "mma.sync.aligned.m16n8k16.row.col.f32." TYPE "." TYPE ".f32 {t0,t1,t2,t3}, {f12,f13,f14,f15}, {%16,%17}, {t0,t1,t2,t3};\n\t" \
+        "fma.rn.f32 %0, %8, t0, %0;\n\t"                                                                    \
+        "fma.rn.f32 %1, %8, t1, %1;\n\t"                                                                    \
+        "fma.rn.f32 %2, %9, t2, %2;\n\t"                                                                    \
+        "fma.rn.f32 %3, %9, t3, %3;\n\t"                                                                    \
+        "}\n"                                                                                               \
+        : "+f"(acc[0]), "+f"(acc[1]), "+f"(acc[2]), "+f"(acc[3])                                            \
+        : "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]), "f"(am[0]), "f"(am[1]), "r"(xr[0]), "r"(xr[1]),       \
+          "r"(xr[2]), "r"(xr[3]), "r"(xr[4]), "r"(xr[5]), "r"(xr[6]), "r"(xr[7]), "r"(lw))
+
+template <typename XT>
+__device__ __forceinline__ void compute_block(float (&acc)[4], const uint32_t (&w)[4], const float (&am)[2],
+                                              const uint32_t (&xr)[8], uint32_t lw);
+template <>
+__device__ __forceinline__ void compute_block<__half>(float (&acc)[4], const uint32_t (&w)[4], const float (&am)[2],
+                                                      const uint32_t (&xr)[8], uint32_t lw) {
+    MPSBNB_COMPUTE_ASM("f16");
+}
+template <>
+__device__ __forceinline__ void compute_block<__nv_bfloat16>(float (&acc)[4], const uint32_t (&w)[4], const float (&am)[2],
+                                                             const uint32_t (&xr)[8], uint32_t lw) {
+    MPSBNB_COMPUTE_ASM("bf16");
+}
+
+// Shared-memory map, in ABSOLUTE shared-window addresses.  The code-pair table sits at exactly
+// 128 KiB so that "table + byte * 256 + lane * 4" is one byte-permute of (weight word, lane word):
+// byte 0 = lane * 4, byte 1 = the weight byte, byte 2 = 0x02 — no addition.  Below it: partial
+// sums, barriers and most ring slots; above it (from 192 KiB) one more slot.
+constexpr uint32_t SG_LUT_ABS = 131072u;
+constexpr uint32_t SG_HIGH_ABS = 196608u;
+constexpr int SG_SMEM_BYTES = 227 * 1024;
+
+struct SlotMap {
+    uint32_t low0, high0, bytes;
+    int nlow, nslots;
+    __device__ __forceinline__ uint32_t addr(int slot) const {
+        return slot < nlow ? low0 + (uint32_t)slot * bytes : high0 + (uint32_t)(slot - nlow) * bytes;
+    }
+};
+
+template <typename XT>
+__global__ void __launch_bounds__(SG_THREADS, 1) gemv4_stream_kernel(const __grid_constant__ StreamArgs a) {
+    extern __shared__ __align__(1024) unsigned char smem[];
+    const uint32_t s_base = smem_u32(smem);
+    const uint32_t s_red = s_base;                                   // 2 x SG_RED_BYTES
+    const uint32_t s_bar = s_base + 2 * SG_RED_BYTES;                // full[8], empty[8], red_full[2], red_empty[2], flag
+    SlotMap sm;
+    sm.bytes = (uint32_t)a.slot_bytes;
+    sm.low0 = (s_bar + 256u + 1023u) & ~1023u;
+    sm.high0 = SG_HIGH_ABS;
+    sm.nlow = (int)((SG_LUT_ABS - sm.low0) / sm.bytes);
+    {
+        const int nhigh = (int)((s_base + (uint32_t)SG_SMEM_BYTES - SG_HIGH_ABS) / sm.bytes);
+        int n = sm.nlow + nhigh;
+        sm.nslots = n > SG_MAX_SLOTS ? SG_MAX_SLOTS : n;
+        if (sm.nlow > sm.nslots) sm.nlow = sm.nslots;
+    }
+    const int nslots = sm.nslots;
+    unsigned char *p_generic0 = smem - s_base;                       // generic pointer of shared address 0
+    volatile uint32_t *abort_flag = reinterpret_cast<volatile uint32_t *>(p_generic0 + s_bar + (2 * SG_MAX_SLOTS + 4) * 8);
+    auto full_bar = [&](int s) { return s_bar + 8u * s; };
+    auto empty_bar = [&](int s) { return s_bar + 8u * (SG_MAX_SLOTS + s); };
+    auto red_full = [&](int b) { return s_bar + 8u * (2 * SG_MAX_SLOTS + b); };
+    auto red_empty = [&](int b) { return s_bar + 8u * (2 * SG_MAX_SLOTS + 2 + b); };
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+
+    if (tid == 0) {
+        for (int s = 0; s < nslots; ++s) { mbar_init(full_bar(s), (a.debug & 2) ? 1 : 2); mbar_init(empty_bar(s), SG_CONSUMERS); }
+        for (int b = 0; b < 2; ++b) { mbar_init(red_full(b), SG_CONSUMERS); mbar_init(red_empty(b), 1); }
+        *abort_flag = 0;
+        fence_mbar_init();
+    }
+    if (warp < 8) {
+        // byte -> (code[low nibble], code[high nibble]) pairs, one replica per lane: entry b of lane l
+        // at table + b * 256 + l * 4.  Warp w fills bytes 32 w .. 32 w + 31.
+        const float my_code = kCode[a.quant_type][lane & 15];
+        const int byte = warp * 32 + lane;
+        const float lo = __shfl_sync(0xffffffffu, my_code, byte & 15);
+        const float hi = __shfl_sync(0xffffffffu, my_code, byte >> 4);
+        const uint32_t mine = pair_bits<XT>(lo, hi);
+#pragma unroll 8
+        for (int j = 0; j < 32; ++j)
+            sts32(SG_LUT_ABS + (uint32_t)((warp * 32 + j) * 256 + lane * 4), __shfl_sync(0xffffffffu, mine, j));
+    } else {
+        // x areas start as zeros: columns beyond K are never written, and 0 * (stale bits) must be 0
+        const int xbytes = (int)sm.bytes - SG_W_BYTES - SG_A_BYTES;
+        for (int s = 0; s < nslots; ++s)
+            for (int o = (tid - 256) * 16; o < xbytes; o += (SG_THREADS - 256) * 16)
+                sts128(sm.addr(s) + SG_W_BYTES + SG_A_BYTES + o, make_uint4(0u, 0u, 0u, 0u));
+    }
+    fence_proxy_async_smem();
+    __syncthreads();
+
+    auto unit_of = [&](int u) -> StreamUnit {
+        if (a.units != nullptr) return a.units[u];
+        StreamUnit un;
+        un.lin = 0; un.row0 = u * SG_ROWS; un.s_begin = 0; un.s_end = (a.one.nb + SG_STAGE_BLOCKS - 1) / SG_STAGE_BLOCKS;
+        return un;
+    };
+    auto lin_of = [&](int i) -> const StreamLinear * { return a.lins != nullptr ? a.lins + i : &a.one; };
+
+    if (warp == SG_CONSUMERS) {
+        // ------------------------------------------------------------ TMA producer: packed weights, and x
+        if (lane == 0) {
+            // A second cursor runs SG_L2_AHEAD stages in front and pulls those boxes into L2, so the
+            // loads into the (small) shared-memory ring see L2 latency, not HBM latency.
+            int pu = blockIdx.x, ps = 0, ps_end = 0, prow0 = 0;
+            const StreamLinear *pL = nullptr;
+            bool phave = false;
+            auto prefetch_one = [&]() {
+                for (;;) {
+                    if (!phave) {
+                        if (pu >= a.nunits) return;
+                        const StreamUnit pn = unit_of(pu);
+                        pL = lin_of(pn.lin); ps = pn.s_begin; ps_end = pn.s_end; prow0 = pn.row0; phave = true;
+                    }
+                    if (ps >= ps_end) { phave = false; pu += gridDim.x; continue; }
+#pragma unroll
+                    for (int p = 0; p < 4; ++p) tma_prefetch_l2_2d(&pL->map, (ps * 4 + p) * 128, prow0);
+                    ++ps;
+                    return;
+                }
+            };
+            if (a.debug & 4)
+                for (int i = 0; i < SG_L2_AHEAD; ++i) prefetch_one();
+            int slot = 0; uint32_t ph = 0;
+            for (int u = blockIdx.x; u < a.nunits && !*abort_flag; u += gridDim.x) {
+                const StreamUnit un = unit_of(u);
+                const StreamLinear *L = lin_of(un.lin);
+                const unsigned char *xb = reinterpret_cast<const unsigned char *>(L->x);
+                for (int s = un.s_begin; s < un.s_end; ++s, slot = (slot + 1 == nslots ? 0 : slot + 1), ph ^= (slot == 0 ? 1u : 0u)) {
+                    if (a.debug & 4) prefetch_one();
+                    if (!mbar_wait_relaxed(empty_bar(slot), ph ^ 1u, abort_flag)) { atomicExch(&g_stream_status, 201); *abort_flag = 1; break; }
+                    const uint32_t dst = sm.addr(slot);
+                    const int k_base = s * (SG_STAGE_BLOCKS * 64);
+                    int xcols = L->K - k_base;                      // x columns of this stage (bulk copies need x_bulk_ok)
+                    xcols = xcols > SG_STAGE_BLOCKS * 64 ? SG_STAGE_BLOCKS * 64 : (xcols < 0 ? 0 : xcols);
+                    const uint32_t xbytes = L->x_bulk_ok ? (uint32_t)xcols * 2u : 0u;
+                    mbar_arrive_expect_tx(full_bar(slot), SG_W_BYTES + xbytes * (uint32_t)a.M);
+#pragma unroll
+                    for (int p = 0; p < 4; ++p)
+                        tma_load_2d(dst + p * 4096, &L->map, full_bar(slot), (s * 4 + p) * 128, un.row0);
+                    if (xbytes != 0u) {
+                        const int64_t col = k_base % L->x_period;
+                        for (int m = 0; m < a.M; ++m)
+                            bulk_load_1d(dst + SG_W_BYTES + SG_A_BYTES + m * SG_XPITCH, xb + ((int64_t)m * L->x_ld + col) * 2,
+                                         xbytes, full_bar(slot));
+                    }
+                }
+            }
+        }
+    } else if (warp == SG_CONSUMERS + 1 + SG_LOADERS) {
+        // ------------------------------------------------------------ reducer: sums the 8 kg partials of a unit
+        // lane = tile row.  MMA row i of row tile rt is tile row 16 rt + rho(i & 7) + 8 (i >> 3).
+        const int rr = lane & 15, v = rr & 7;
+        const int i = ((v >> 1) + 4 * (v & 1)) + 8 * (rr >> 3);
+        const int wrt = lane >> 4;
+        int uc = 0;
+        for (int u = blockIdx.x; u < a.nunits && !*abort_flag; u += gridDim.x, ++uc) {
+            const StreamUnit un = unit_of(u);
+            const StreamLinear *L = lin_of(un.lin);
+            const int buf = uc & 1;
+            if (!mbar_wait_relaxed(red_full(buf), (uint32_t)(uc >> 1) & 1u, abort_flag)) { atomicExch(&g_stream_status, 204); *abort_flag = 1; break; }
+            const float *red = reinterpret_cast<const float *>(p_generic0 + s_red + buf * SG_RED_BYTES);
+            const int n = un.row0 + lane;
+            for (int m = 0; m < a.M; ++m) {
+                float sum = 0.0f;
+#pragma unroll
+                for (int k8 = 0; k8 < 8; ++k8) sum += red[((k8 * 2 + wrt) * 8 + m) * 20 + i];
+                if (n < L->N) {
+                    if (L->bias != nullptr && un.s_begin == 0) sum += to_f32<XT>(reinterpret_cast<const XT *>(L->bias)[n]);
+                    const int64_t o = (int64_t)m * L->N + n;
+                    if (L->acc != nullptr) atomicAdd(L->acc + o, sum);
+                    else if (L->y_dtype == MPSBNB_F16) reinterpret_cast<__half *>(L->y)[o] = __float2half_rn(sum);
+                    else if (L->y_dtype == MPSBNB_BF16) reinterpret_cast<__nv_bfloat16 *>(L->y)[o] = __float2bfloat16_rn(sum);
+                    else reinterpret_cast<float *>(L->y)[o] = sum;
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(red_empty(buf));
+        }
+    } else if (warp > SG_CONSUMERS) {
+        // ------------------------------------------------------------ loaders: block scales (and x when it cannot be bulk-copied)
+        // SG_LOADERS warps take stages in turn; each reads the scales of its NEXT stage before it
+        // stores the current one, so two rounds of global loads are in flight per warp.
+        const int me = warp - SG_CONSUMERS - 1;
+        if (a.debug & 2) return;   // DEBUGVAR
+        auto read_scales = [&](const StreamLinear *L, int row0, int s, float (&sc)[16]) {
+            const int n = row0 + lane;
+            const int b0 = s * SG_STAGE_BLOCKS;
+            const int64_t i0 = (int64_t)n * L->nb + b0;
+            if (n >= L->N) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) sc[j] = 0.0f;
+            } else if (L->absmax2 == nullptr) {
+                const float *am = reinterpret_cast<const float *>(L->absmax);
+                if (b0 + 16 <= L->nb && (i0 & 3) == 0) {
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const float4 v = __ldg(reinterpret_cast<const float4 *>(am + i0) + q);
+                        sc[4 * q] = v.x; sc[4 * q + 1] = v.y; sc[4 * q + 2] = v.z; sc[4 * q + 3] = v.w;
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) sc[j] = (b0 + j < L->nb) ? __ldg(am + i0 + j) : 0.0f;
+                }
+            } else {
+                // int8 code * (second-level maximum / 127); 16 consecutive blocks see at most two maxima
+                const int8_t *aq = reinterpret_cast<const int8_t *>(L->absmax);
+                const int last = (b0 + 15 < L->nb ? b0 + 15 : L->nb - 1) - b0;
+                const float f0 = __ldg(L->absmax2 + (i0 >> 8)) * (1.0f / 127.0f);
+                const float f1 = __ldg(L->absmax2 + ((i0 + last) >> 8)) * (1.0f / 127.0f);
+                const int split = (int)(((i0 >> 8) + 1) * 256 - i0);          // first j that uses f1
+                uint32_t raw[4];
+                if (b0 + 16 <= L->nb && (i0 & 3) == 0) {
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) raw[q] = __ldg(reinterpret_cast<const uint32_t *>(aq + i0) + q);
+                } else {
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        raw[q] = 0u;
+#pragma unroll
+                        for (int e = 0; e < 4; ++e)
+                            if (b0 + 4 * q + e < L->nb) raw[q] |= (uint32_t)(uint8_t)__ldg(aq + i0 + 4 * q + e) << (8 * e);
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const int code = (int)(int8_t)((raw[j >> 2] >> (8 * (j & 3))) & 0xFFu);
+                    sc[j] = (b0 + j < L->nb) ? (float)code * (j < split ? f0 : f1) : 0.0f;
+                }
+            }
+        };
+        // walk the global stage sequence; (u, s) of my next stage is found by stepping the cursor
+        int u = blockIdx.x;
+        StreamUnit un = {0, 0, 0, 0};
+        const StreamLinear *L = nullptr;
+        int s = 0, slot = 0, turn = 0;       // turn: global stage index modulo SG_LOADERS
+        uint32_t ph = 0;
+        bool have = false;
+        auto step = [&]() {                  // to the next stage of the global sequence
+            ++s;
+            if (++turn == SG_LOADERS) turn = 0;
+            if (++slot == nslots) { slot = 0; ph ^= 1u; }
+        };
+        auto advance_to_mine = [&]() {       // positions the cursor on my next stage; returns false at the end
+            for (;;) {
+                if (!have) {
+                    if (u >= a.nunits) return false;
+                    un = unit_of(u); L = lin_of(un.lin); s = un.s_begin; have = true;
+                }
+                if (s >= un.s_end) { have = false; u += gridDim.x; continue; }
+                if (turn == me) return true;
+                step();
+            }
+        };
+        float cur[16];
+        bool more = advance_to_mine();
+        if (more) read_scales(L, un.row0, s, cur);
+        while (more && !*abort_flag) {
+            const int my_slot = slot, my_s = s;
+            const uint32_t my_ph = ph;
+            const StreamLinear *my_L = L;
+            step();
+            float nxt[16];
+            more = advance_to_mine();
+            if (more) read_scales(L, un.row0, s, nxt);
+            if (!mbar_wait_relaxed(empty_bar(my_slot), my_ph ^ 1u, abort_flag)) { atomicExch(&g_stream_status, 202); *abort_flag = 1; break; }
+            const uint32_t sb = sm.addr(my_slot);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) sts_f32(sb + SG_W_BYTES + (j * 32 + lane) * 4, cur[j]);
+            if (!my_L->x_bulk_ok) {
+                // x: 1024 columns of every batch row, zero beyond K
+                const XT *x = reinterpret_cast<const XT *>(my_L->x);
+                const int k_base = my_s * (SG_STAGE_BLOCKS * 64);
+                for (int m = 0; m < a.M; ++m) {
+                    const XT *xr = x + (int64_t)m * my_L->x_ld;
+#pragma unroll
+                    for (int c4 = 0; c4 < 4; ++c4) {
+                        const int k0 = k_base + (lane + 32 * c4) * 8;
+                        uint16_t e[8];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j)
+                            e[j] = (k0 + j < my_L->K) ? *reinterpret_cast<const uint16_t *>(xr + (k0 + j) % my_L->x_period) : (uint16_t)0;
+                        sts128(sb + SG_W_BYTES + SG_A_BYTES + m * SG_XPITCH + (lane + 32 * c4) * 16,
+                               make_uint4(e[0] | ((uint32_t)e[1] << 16), e[2] | ((uint32_t)e[3] << 16),
+                                          e[4] | ((uint32_t)e[5] << 16), e[6] | ((uint32_t)e[7] << 16)));
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(full_bar(my_slot));
+#pragma unroll
+            for (int j = 0; j < 16; ++j) cur[j] = nxt[j];
+        }
+    } else {
+        // ------------------------------------------------------------ consumers
+        const int g = lane >> 2, t = lane & 3;
+        const int rt = warp & 1, kg = warp >> 1;
+        const int rho = ((2 * g) & 7) + (g >> 2);                // tile row of MMA row g (conflict-free permutation)
+        const uint32_t lane_word = SG_LUT_ABS | ((uint32_t)lane * 4u);   // bytes 0, 2, 3 of every table address
+        uint32_t woff[2], xoff[2], aoff[2];
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const int blk = 2 * kg + j;
+            const int box = blk >> 2, c = 2 * (blk & 3) + (t >> 1);
+            const int r0 = 16 * rt + rho;
+            woff[j] = (uint32_t)(box * 4096 + r0 * 128 + ((c ^ rho) << 4) + 8 * (t & 1));
+            xoff[j] = (uint32_t)(SG_W_BYTES + SG_A_BYTES + g * SG_XPITCH + (blk * 64 + 16 * t) * 2);
+            aoff[j] = (uint32_t)(SG_W_BYTES + (blk * 32 + r0) * 4);
+        }
+        const uint32_t hasx = g < a.M ? 1u : 0u;
+        uint32_t xr0[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u}, xr1[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
+        int slot = 0, uc = 0;
+        uint32_t ph = 0, sb = sm.addr(0);
+        for (int u = blockIdx.x; u < a.nunits && !*abort_flag; u += gridDim.x, ++uc) {
+            const StreamUnit un = unit_of(u);
+            const int nbv = lin_of(un.lin)->nbv;
+            float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            bool ok = true;
+            for (int s = un.s_begin; s < un.s_end; ++s) {
+                if (!mbar_wait(full_bar(slot), ph, abort_flag)) { atomicExch(&g_stream_status, 203); *abort_flag = 1; ok = false; break; }
+                const int nvalid = nbv - (s * SG_STAGE_BLOCKS + 2 * kg);   // my blocks that hold real k (warp-uniform)
+                uint32_t w0[4], w1[4];
+                float am0[2], am1[2];
+                fetch_block(w0, am0, xr0, sb, woff[0], aoff[0], xoff[0], hasx);
+                fetch_block(w1, am1, xr1, sb, woff[1], aoff[1], xoff[1], hasx);
+                // the slot goes back to the producers as soon as its bytes are in registers: the arrive is
+                // queued behind the loads and, through `dep`, cannot issue before the last of them returned
+                const uint32_t dep = (w1[3] | __float_as_uint(am1[1])) & a.zero;
+                __syncwarp();
+                if (lane == 0) mbar_arrive(empty_bar(slot) + dep);
+                if (!(a.debug & 1)) {
+                    if (nvalid > 0) compute_block<XT>(acc, w0, am0, xr0, lane_word);
+                    if (nvalid > 1) compute_block<XT>(acc, w1, am1, xr1, lane_word);
+                }
+                if (++slot == nslots) { slot = 0; ph ^= 1u; }
+                sb = sm.addr(slot);
+            }
+            if (!ok) break;
+            // hand the partial sums to the reducer warp; the buffer of two units ago must have been drained
+            const int buf = uc & 1;
+            if (!mbar_wait(red_empty(buf), ((uint32_t)(uc >> 1) & 1u) ^ 1u, abort_flag)) { atomicExch(&g_stream_status, 205); *abort_flag = 1; break; }
+            const uint32_t rb = s_red + (uint32_t)(buf * SG_RED_BYTES);
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+                sts_f32(rb + (uint32_t)(((warp * 8 + 2 * t + (c & 1)) * 20 + g + 8 * (c >> 1)) * 4), acc[c]);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(red_full(buf));
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// host side
+// ------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled() {
+    static EncodeTiledFn fn = nullptr;
+    if (fn == nullptr) {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+struct HostLinear {
+    const void *x; int64_t x_ld; int64_t x_period; const uint8_t *packed; const void *absmax; const float *absmax2;
+    const void *bias; void *y; float *acc; int64_t N, K;
+};
+
+static int fill_linear(StreamLinear &L, const HostLinear &h, int y_dtype) {
+    if (h.N <= 0 || h.K <= 0 || h.N > 0x7fffffff || h.K > 0x7fffffff) return MPSBNB_ERR_INVALID_ARG;
+    if (h.x == nullptr || h.packed == nullptr || h.absmax == nullptr || (h.y == nullptr && h.acc == nullptr)) return MPSBNB_ERR_INVALID_ARG;
+    if (!aligned16(h.packed)) return MPSBNB_ERR_INVALID_ARG;
+    EncodeTiledFn fn = encode_tiled();
+    if (fn == nullptr) return MPSBNB_ERR_NO_DEVICE;
+    const int64_t Kp = padded_k(h.K, 64);
+    const cuuint64_t dims[2] = {(cuuint64_t)(Kp / 2), (cuuint64_t)h.N};
+    const cuuint64_t strides[1] = {(cuuint64_t)(Kp / 2)};
+    const cuuint32_t box[2] = {128u, (cuuint32_t)SG_ROWS};
+    const cuuint32_t estr[2] = {1u, 1u};
+    if (fn(&L.map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t *>(h.packed), dims, strides, box, estr,
+           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return MPSBNB_ERR_INVALID_ARG;
+    L.x = h.x; L.absmax = h.absmax; L.absmax2 = h.absmax2; L.bias = h.bias; L.y = h.y; L.acc = h.acc;
+    L.x_ld = h.x_ld;
+    L.N = (int)h.N; L.K = (int)h.K; L.nb = (int)(Kp / 64); L.nbv = (int)((h.K + 63) / 64);
+    L.x_period = (int)(h.x_period > 0 ? h.x_period : h.K);
+    L.y_dtype = y_dtype;
+    L.x_vec_ok = (h.x_ld % 8 == 0) && (L.x_period % 8 == 0) && (h.K % 8 == 0) && aligned16(h.x);
+    L.x_bulk_ok = L.x_vec_ok && (L.x_period >= L.K || L.x_period % (SG_STAGE_BLOCKS * 64) == 0);
+    return MPSBNB_OK;
+}
+
+static int slot_bytes_for(int M) { return SG_W_BYTES + SG_A_BYTES + ((M * SG_XPITCH + 1023) / 1024) * 1024; }
+
+// lower bound of the slot count the kernel will find (it derives the exact map from its shared base)
+static int slots_for(int M) {
+    const int low = (128 * 1024 - 2 * SG_RED_BYTES - 256 - 2048) / slot_bytes_for(M);
+    const int high = (227 * 1024 - 192 * 1024) / slot_bytes_for(M);
+    const int n = low + high;
+    return n > SG_MAX_SLOTS ? SG_MAX_SLOTS : n;
+}
+
+template <typename XT>
+static int launch_stream(StreamArgs &args, cudaStream_t st) {
+    args.slot_bytes = slot_bytes_for(args.M);
+    { const char *e = getenv("MPSBNB_STREAM_DEBUG"); args.debug = e ? atoi(e) : 0; }   // DEBUGVAR
+    args.zero = 0u;
+    args.nslots = slots_for(args.M);
+    if (args.nslots < 2) return MPSBNB_ERR_UNSUPPORTED;
+    const int smem = SG_SMEM_BYTES;
+    static int configured[64] = {};
+    int dev = 0;
+    MPSBNB_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64 || configured[dev] < smem) {
+        MPSBNB_CUDA_TRY(cudaFuncSetAttribute(gemv4_stream_kernel<XT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+        if (dev >= 0 && dev < 64) configured[dev] = 227 * 1024;
+    }
+    int grid = sm_count();
+    if (grid > args.nunits) grid = args.nunits;
+    gemv4_stream_kernel<XT><<<grid, SG_THREADS, smem, st>>>(args);
+    return check_launch();
+}
+
+int stream_status_fetch(int *out, bool reset) {
+    MPSBNB_CUDA_TRY(cudaMemcpyFromSymbol(out, g_stream_status, sizeof(int)));
+    if (reset) {
+        const int zero = 0;
+        MPSBNB_CUDA_TRY(cudaMemcpyToSymbol(g_stream_status, &zero, sizeof(int)));
+    }
+    return MPSBNB_OK;
+}
+
+// Single linear, M <= 8 (called from mpsbnb_gemv_4bit).
+int gemv4_stream_single(const void *x, int x_dtype, int64_t M, const uint8_t *packed, const void *absmax,
+                        const float *absmax2, int64_t N, int64_t K, int quant_type, const void *bias, void *y,
+                        int y_dtype, cudaStream_t st) {
+    StreamArgs args;
+    args.lins = nullptr; args.units = nullptr;
+    HostLinear h{x, K, K, packed, absmax, absmax2, bias, y, nullptr, N, K};
+    int rc = fill_linear(args.one, h, y_dtype);
+    if (rc != MPSBNB_OK) return rc;
+    args.nunits = (int)((N + SG_ROWS - 1) / SG_ROWS);
+    args.M = (int)M; args.quant_type = quant_type;
+    return x_dtype == MPSBNB_F16 ? launch_stream<__half>(args, st) : launch_stream<__nv_bfloat16>(args, st);
+}
+
+}  // namespace mpsbnb
+
+using namespace mpsbnb;
+
+// ------------------------------------------------------------------------------------------
+// grouped launches: a plan (device memory supplied by the caller) holds the linears and units
+// ------------------------------------------------------------------------------------------
+static inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+static int count_units(const mpsbnb_linear4_desc *d, int n, int chunk_stages) {
+    int64_t total = 0;
+    for (int i = 0; i < n; ++i) {
+        const int64_t S = (padded_k(d[i].K, 64) / 64 + SG_STAGE_BLOCKS - 1) / SG_STAGE_BLOCKS;
+        const int64_t chunks = d[i].acc != nullptr ? (S + chunk_stages - 1) / chunk_stages : 1;
+        total += ((d[i].N + SG_ROWS - 1) / SG_ROWS) * chunks;
+    }
+    return total > 0x7fffffff ? -1 : (int)total;
+}
+
+extern "C" size_t mpsbnb_gemv_4bit_group_plan_bytes(const mpsbnb_linear4_desc *descs, int n_linears) {
+    if (descs == nullptr || n_linears <= 0) return 0;
+    const int nu = count_units(descs, n_linears, 4);
+    if (nu < 0) return 0;
+    return align_up(sizeof(StreamLinear) * (size_t)n_linears, 256) + align_up(sizeof(StreamUnit) * (size_t)nu, 256);
+}
+
+extern "C" int mpsbnb_gemv_4bit_group_plan(const mpsbnb_linear4_desc *descs, int n_linears, int64_t M, int x_dtype,
+                                           int y_dtype, int quant_type, void *plan_dev, size_t plan_bytes,
+                                           mpsbnb_group_plan *plan_out, void *stream) {
+    if (descs == nullptr || n_linears <= 0 || plan_dev == nullptr || plan_out == nullptr) return MPSBNB_ERR_INVALID_ARG;
+    if (!is_16bit(x_dtype) || !valid_dtype(y_dtype) || (quant_type != MPSBNB_NF4 && quant_type != MPSBNB_FP4)) return MPSBNB_ERR_INVALID_ARG;
+    if (M <= 0 || M > SG_MAX_M) return MPSBNB_ERR_UNSUPPORTED;
+    if ((reinterpret_cast<uintptr_t>(plan_dev) & 255) != 0) return MPSBNB_ERR_INVALID_ARG;
+    const int chunk = 4;
+    const int nu = count_units(descs, n_linears, chunk);
+    if (nu <= 0) return MPSBNB_ERR_INVALID_ARG;
+    const size_t lin_bytes = align_up(sizeof(StreamLinear) * (size_t)n_linears, 256);
+    const size_t need = lin_bytes + align_up(sizeof(StreamUnit) * (size_t)nu, 256);
+    if (plan_bytes < need) return MPSBNB_ERR_WORKSPACE;
+    unsigned char *host = (unsigned char *)malloc(need);
+    if (host == nullptr) return MPSBNB_ERR_INVALID_ARG;
+    memset(host, 0, need);
+    StreamLinear *lins = reinterpret_cast<StreamLinear *>(host);
+    StreamUnit *units = reinterpret_cast<StreamUnit *>(host + lin_bytes);
+    int rc = MPSBNB_OK;
+    for (int i = 0; i < n_linears && rc == MPSBNB_OK; ++i) {
+        HostLinear h{descs[i].x, descs[i].x_ld, descs[i].x_period, descs[i].packed, descs[i].absmax, descs[i].absmax2,
+                     descs[i].bias, descs[i].y, descs[i].acc, descs[i].N, descs[i].K};
+        rc = fill_linear(lins[i], h, y_dtype);
+    }
+    if (rc == MPSBNB_OK) {
+        // units, longest first so that the round-robin remainder consists of the short ones
+        int nu2 = 0;
+        for (int pass = chunk * 8; pass >= 1; --pass) {
+            for (int i = 0; i < n_linears; ++i) {
+                const int S = (lins[i].nb + SG_STAGE_BLOCKS - 1) / SG_STAGE_BLOCKS;
+                const int step = lins[i].acc != nullptr ? chunk : S;
+                for (int s0 = 0; s0 < S; s0 += step) {
+                    const int s1 = s0 + step < S ? s0 + step : S;
+                    const int len = s1 - s0 > chunk * 8 ? chunk * 8 : s1 - s0;
+                    if (len != pass) continue;
+                    for (int r0 = 0; r0 < lins[i].N; r0 += SG_ROWS) units[nu2++] = StreamUnit{i, r0, s0, s1};
+                }
+            }
+        }
+        if (nu2 != nu) rc = MPSBNB_ERR_INVALID_ARG;
+    }
+    if (rc == MPSBNB_OK) {
+        cudaStream_t st = (cudaStream_t)stream;
+        cudaError_t e = cudaMemcpyAsync(plan_dev, host, need, cudaMemcpyHostToDevice, st);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+        if (e != cudaSuccess) rc = record_cuda_error(e);
+    }
+    free(host);
+    if (rc != MPSBNB_OK) return rc;
+    plan_out->dev = plan_dev;
+    plan_out->units_offset = (int64_t)lin_bytes;
+    plan_out->n_linears = n_linears;
+    plan_out->n_units = nu;
+    plan_out->M = (int)M;
+    plan_out->x_dtype = x_dtype;
+    plan_out->quant_type = quant_type;
+    plan_out->reserved = 0;
+    return MPSBNB_OK;
+}
+
+extern "C" int mpsbnb_gemv_4bit_group_run(const mpsbnb_group_plan *plan, void *stream) {
+    if (plan == nullptr || plan->dev == nullptr || plan->n_units <= 0) return MPSBNB_ERR_INVALID_ARG;
+    StreamArgs args;
+    memset(&args, 0, sizeof(args));
+    args.lins = reinterpret_cast<const StreamLinear *>(plan->dev);
+    args.units = reinterpret_cast<const StreamUnit *>(reinterpret_cast<const unsigned char *>(plan->dev) + plan->units_offset);
+    args.nunits = plan->n_units; args.M = plan->M; args.quant_type = plan->quant_type;
+    return plan->x_dtype == MPSBNB_F16 ? launch_stream<__half>(args, (cudaStream_t)stream)
+                                       : launch_stream<__nv_bfloat16>(args, (cudaStream_t)stream);
+}

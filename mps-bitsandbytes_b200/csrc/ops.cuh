@@ -17,4 +17,9 @@ int gemm_16bit(const void *a, int64_t lda, const void *b, int64_t ldb, int ab_dt
                const float *row_scale, const float *col_scale, const void *bias, int bias_dtype, void *y, int64_t ldy,
                int y_dtype, cudaStream_t st);
 
+int gemv4_stream_single(const void *x, int x_dtype, int64_t M, const uint8_t *packed, const void *absmax,
+                        const float *absmax2, int64_t N, int64_t K, int quant_type, const void *bias, void *y,
+                        int y_dtype, cudaStream_t st);
+int stream_status_fetch(int *out, bool reset);
+
 }  // namespace mpsbnb

@@ -39,18 +39,33 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+// try_wait that may suspend the thread in hardware for up to `ns` nanoseconds before it
+// reports "not yet": a waiting warp then takes no issue slots.
+__device__ __forceinline__ bool mbar_try_wait_suspend(uint32_t bar, uint32_t parity, uint32_t ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity), "r"(ns)
+        : "memory");
+    return ok != 0;
+}
 // Waits for the phase with the given parity, for at most ~`limit_cycles` SM clocks (about a
 // second), or until another role of the CTA raises `abort_flag`.  Returns false in both
 // cases; callers then record a status word and leave their loops — no wait in this library
-// spins without a bound.
+// is unbounded.  The slow path parks the thread in the barrier hardware between checks.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag,
                                           long long limit_cycles = 2000000000ll) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
-    while (!mbar_try_wait(bar, parity)) {
+    while (!mbar_try_wait_suspend(bar, parity, 20000u)) {
         if (*abort_flag != 0 || clock64() - t0 > limit_cycles) return false;
     }
     return true;
+}
+// Alias kept for the roles off the critical path (same wait; the suspend makes a back-off loop unnecessary).
+__device__ __forceinline__ bool mbar_wait_relaxed(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag) {
+    return mbar_wait(bar, parity, abort_flag);
 }
 
 // generic-proxy writes (st.shared) made visible to the async proxy (TMA, tcgen05.mma)
@@ -69,6 +84,11 @@ __device__ __forceinline__ void bulk_load_1d(uint32_t dst_smem, const void *src,
         "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
         ::"r"(dst_smem), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(bar)
         : "memory");
+}
+// Brings the box into L2 only (no shared-memory destination, no barrier).
+__device__ __forceinline__ void tma_prefetch_l2_2d(const CUtensorMap *map, int x, int y) {
+    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global [%0, {%1, %2}];"
+                 ::"l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y) : "memory");
 }
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap *map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");

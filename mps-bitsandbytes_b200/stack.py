@@ -71,6 +71,21 @@ def algorithmic_bytes(cfg: StackConfig, M: int, double_quant: bool = True, layer
     return weight_bytes(cfg, double_quant, layers) + act * L
 
 
+def shard_rows(n: int, rank: int, world: int):
+    """Row range [lo, hi) of an [n, k] weight (and of its packed bytes / absmax rows) owned by ``rank``."""
+    if n % world:
+        raise ValueError(f"{n} rows do not divide over {world} ranks")
+    ns = n // world
+    return rank * ns, (rank + 1) * ns
+
+
+def gathered_to_full(gathered: torch.Tensor) -> torch.Tensor:
+    """[g, M, H/g] (what all_gather_into_tensor returns for per-rank [M, H/g] shards) -> [M, H].
+    The device path does this inside mpsbnb_stack_expand; this is its host-side statement."""
+    g, M, hs = gathered.shape
+    return gathered.permute(1, 0, 2).reshape(M, g * hs)
+
+
 class _Proj:
     __slots__ = ("name", "n", "k", "packed", "absmax", "absmax2", "state")
 
@@ -93,14 +108,15 @@ class LayerStack:
         for l in range(self.layers):
             row = []
             for i, (name, n, k) in enumerate(cfg.projections()):
-                ns = n // world
-                if (ns * (k // 64)) % 256 and double_quant:
+                lo, hi = shard_rows(n, rank, world)
+                ns = hi - lo
+                if (ns * (k // 64)) % 256 and double_quant and world > 1:
                     raise ValueError("shard does not align with the 256-block groups of double quantisation")
                 # the whole weight is drawn from the (layer, projection) seed, N(0, 0.02), and this
                 # rank keeps its rows: the model is the same for every world size
                 gen.manual_seed(seed + 7 * l + i)
                 full = torch.randn(n, k, device=self.device, generator=gen, dtype=torch.float32)
-                w = (full[rank * ns:(rank + 1) * ns] * 0.02).to(dtype)
+                w = (full[lo:hi] * 0.02).to(dtype)
                 del full
                 packed, st = quantize_4bit(w, blocksize=64, compress_statistics=double_quant, quant_type=quant_type)
                 del w
@@ -120,7 +136,40 @@ class LayerStack:
         self.out = {name: torch.zeros(M, n // g, dtype=dt, device=dev) for name, n, _ in cfg.projections()}
         self.h_shard = torch.zeros(M, cfg.hidden // g, dtype=dt, device=dev)
         self.gathered = torch.zeros(g, M, cfg.hidden // g, dtype=dt, device=dev) if g > 1 else None
+        self.acc = torch.zeros(M, cfg.hidden // g, dtype=torch.float32, device=dev)
         self._M = M
+        self._plans = None
+        if M <= 8:
+            self._build_plans(M)
+
+    def _build_plans(self, M: int):
+        """One grouped-launch plan per layer: q, k, v, gate, up store their outputs; o and down add
+        into the fp32 accumulator ``acc`` (their sum is what the boundary needs); down reads h with
+        its column index wrapped at H, which is the tiled input e without materialising it."""
+        cfg, lib, g = self.cfg, N.lib(), self.world
+        self._plans, self._plan_mem = [], []
+        for l in range(self.layers):
+            descs = (N.Linear4Desc * 7)()
+            for i, pr in enumerate(self.proj[l]):
+                d = descs[i]
+                d.x, d.x_ld = self.h.data_ptr(), cfg.hidden
+                d.x_period = cfg.hidden if pr.name == "down" else 0
+                d.packed, d.absmax = pr.packed.data_ptr(), pr.absmax.data_ptr()
+                d.absmax2 = None if pr.absmax2 is None else pr.absmax2.data_ptr()
+                d.bias = None
+                if pr.name in ("o", "down"):
+                    d.y, d.acc = None, self.acc.data_ptr()
+                else:
+                    d.y, d.acc = self.out[pr.name].data_ptr(), None
+                d.N, d.K = pr.n, pr.k
+            nbytes = lib.mpsbnb_gemv_4bit_group_plan_bytes(descs, C.c_int(7))
+            mem = torch.empty(nbytes, dtype=torch.uint8, device=self.device)
+            plan = N.GroupPlan()
+            N.check(lib.mpsbnb_gemv_4bit_group_plan(descs, C.c_int(7), N.i64(M), N.dt(self.dtype), N.dt(self.dtype),
+                                                    C.c_int(N.qt(self.quant_type)), N.ptr(mem), C.c_size_t(nbytes),
+                                                    C.byref(plan), N.stream()), "gemv_4bit_group_plan")
+            self._plans.append(plan)
+            self._plan_mem.append(mem)
 
     def _gemv(self, pr: _Proj, x: torch.Tensor, y: torch.Tensor, M: int):
         lib = N.lib()
@@ -138,6 +187,19 @@ class LayerStack:
     def _run_layers(self, M: int):
         """Enqueue one step (all layers) on the current stream."""
         cfg, lib, g = self.cfg, N.lib(), self.world
+        if self._plans is not None:
+            hs = cfg.hidden // g
+            for l in range(self.layers):
+                N.check(lib.mpsbnb_gemv_4bit_group_run(C.byref(self._plans[l]), N.stream()), "gemv_4bit_group_run")
+                dst = self.h if g == 1 else self.h_shard
+                N.check(lib.mpsbnb_stack_boundary_acc(N.ptr(self.acc), C.c_float(self.alpha), N.i64(M * hs), N.ptr(dst),
+                                                      N.dt(self.dtype), N.stream()), "stack_boundary_acc")
+                if g > 1:
+                    torch.distributed.all_gather_into_tensor(self.gathered.view(g * M, -1), self.h_shard, group=self.group)
+                    N.check(lib.mpsbnb_stack_expand(N.ptr(self.gathered), N.dt(self.dtype), N.i64(g), N.i64(M),
+                                                    N.i64(cfg.hidden), N.i64(cfg.hidden), N.ptr(self.h), None,
+                                                    N.stream()), "stack_expand")
+            return
         for l in range(self.layers):
             for pr in self.proj[l]:
                 self._gemv(pr, self.e if pr.name == "down" else self.h, self.out[pr.name], M)
@@ -150,7 +212,7 @@ class LayerStack:
                 N.check(lib.mpsbnb_stack_boundary(N.ptr(self.out["o"]), N.ptr(self.out["down"]), N.dt(self.dtype),
                                                   C.c_float(self.alpha), N.i64(M), N.i64(hs), N.i64(hs),
                                                   N.ptr(self.h_shard), None, N.stream()), "stack_boundary")
-                torch.distributed.all_gather_into_tensor(self.gathered, self.h_shard, group=self.group)
+                torch.distributed.all_gather_into_tensor(self.gathered.view(g * M, -1), self.h_shard, group=self.group)
                 N.check(lib.mpsbnb_stack_expand(N.ptr(self.gathered), N.dt(self.dtype), N.i64(g), N.i64(M),
                                                 N.i64(cfg.hidden), N.i64(cfg.ffn), N.ptr(self.h), N.ptr(self.e),
                                                 N.stream()), "stack_expand")
@@ -203,5 +265,7 @@ class LayerStack:
         return self.h
 
     def launches_per_step(self) -> int:
-        per_layer = 7 + (1 if self.world == 1 else 2)
-        return 1 + self.layers * per_layer
+        """Kernels of this library launched per step (NCCL's own kernels not counted)."""
+        if self._plans is not None:
+            return 1 + self.layers * (2 if self.world == 1 else 3)
+        return 1 + self.layers * (7 + (1 if self.world == 1 else 2))

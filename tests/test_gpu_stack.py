@@ -1,0 +1,64 @@
+"""GPU parity of the layer stack (grouped streaming GEMV for batch <= 8, per-linear kernels above)
+against the oracle running the same dataflow on the weights read back from the device."""
+import numpy as np
+import pytest
+import torch
+
+from mps_bitsandbytes_b200 import stack as S
+from oracle import oracle_np as O
+from gpu_util import assert_device_ok, rel_err, to_np
+
+pytestmark = pytest.mark.gpu
+
+
+def oracle_stack(st: S.LayerStack, x: np.ndarray):
+    cfg = st.cfg
+    h = x.astype(np.float16)
+    outs = {}
+    for l in range(st.layers):
+        e = np.tile(h, (1, -(-cfg.ffn // cfg.hidden)))[:, :cfg.ffn]
+        y = {}
+        for pr in st.proj[l]:
+            a2 = None if pr.absmax2 is None else to_np(pr.absmax2)
+            w = O.dequantize_4bit(to_np(pr.packed), to_np(pr.absmax), (pr.n, pr.k), 64, st.quant_type, "float16", a2)
+            xin = e if pr.name == "down" else h
+            y[pr.name] = xin.astype(np.float32) @ w.astype(np.float32).T
+        outs = {k: v.astype(np.float16) for k, v in y.items()}
+        h = (np.float32(st.alpha) * (y["o"] + y["down"])).astype(np.float16)
+    return h, outs
+
+
+@pytest.mark.parametrize("M", [1, 3, 8, 16])
+@pytest.mark.parametrize("qt,dq", [("nf4", True), ("fp4", False)])
+def test_small_stack_matches_oracle(M, qt, dq):
+    cfg = S.StackConfig("tiny", hidden=256, ffn=704, kv=64, layers=3)
+    st = S.LayerStack(cfg, device="cuda:0", quant_type=qt, double_quant=dq, seed=5)
+    rng = np.random.default_rng(M)
+    x = rng.standard_normal((M, cfg.hidden)).astype(np.float16)
+    for use_graph in (False, True):
+        st.prepare(M, use_graph=use_graph)
+        h = st.step(torch.from_numpy(x).cuda())
+        torch.cuda.synchronize()
+        ref_h, ref_out = oracle_stack(st, x)
+        assert rel_err(to_np(h), ref_h) <= 1e-2, (use_graph, rel_err(to_np(h), ref_h))
+        for name in ("q", "k", "v", "gate", "up"):
+            assert rel_err(to_np(st.out[name]), ref_out[name]) <= 1e-2, name
+        # a second step from the same input gives the same answer (accumulators were re-armed)
+        h2 = st.step(torch.from_numpy(x).cuda()).clone()
+        torch.cuda.synchronize()
+        assert rel_err(to_np(h2), ref_h) <= 1e-2
+    assert_device_ok()
+
+
+def test_llama7b_layer_shapes_one_layer():
+    """One layer at the real Llama-2-7B widths, batch 1 (the benchmark's unit of work)."""
+    st = S.LayerStack(S.LLAMA2_7B, device="cuda:0", layers=1, seed=9)
+    st.prepare(1, use_graph=False)
+    rng = np.random.default_rng(0)
+    x = rng.standard_normal((1, 4096)).astype(np.float16)
+    h = st.step(torch.from_numpy(x).cuda())
+    torch.cuda.synchronize()
+    ref_h, ref_out = oracle_stack(st, x)
+    assert rel_err(to_np(h), ref_h) <= 1e-2
+    assert rel_err(to_np(st.out["gate"]), ref_out["gate"]) <= 1e-2
+    assert_device_ok()
