@@ -131,8 +131,14 @@ typedef struct mpsbnb_linear4_desc {
 typedef struct mpsbnb_group_plan {
     void *dev;
     int64_t units_offset;
-    int n_linears, n_units, M, x_dtype, quant_type, reserved;
+    int n_linears, n_units, M, x_dtype, quant_type;
+    int flags;               /* set by the caller before a run: MPSBNB_GROUP_PDL or 0 */
 } mpsbnb_group_plan;
+
+/* Launch with programmatic dependent launch: the kernel may start (build its tables, fetch
+ * weights) while the previous kernel in the stream is still finishing, and waits for that
+ * kernel before it reads x or writes results.  Use when the previous kernel produces x. */
+#define MPSBNB_GROUP_PDL 1
 
 size_t mpsbnb_gemv_4bit_group_plan_bytes(const mpsbnb_linear4_desc *descs, int n_linears);
 /* Builds the plan (synchronises the stream once: it uploads the tables). */
@@ -151,7 +157,8 @@ int mpsbnb_stack_boundary(const void *o, const void *d, int dtype, float alpha, 
 /* Boundary for the grouped path, where o and down were atomically accumulated into one fp32
  * matrix: h[i] = alpha * acc[i] (i < n, rounded to dtype) and acc[i] = 0.
  * No reference counterpart. */
-int mpsbnb_stack_boundary_acc(float *acc, float alpha, int64_t n, void *h, int dtype, void *stream);
+int mpsbnb_stack_boundary_acc(float *acc, float alpha, int64_t n, void *h, int dtype, int flags,
+                              void *stream);   /* flags: MPSBNB_GROUP_PDL or 0 */
 
 /* Multi-GPU form of the boundary: G[r][m][c] holds the all-gathered per-rank shards of the
  * new h (c < H / nranks); writes h[m, r*H/nranks + c] = G[r][m][c] and e as above.

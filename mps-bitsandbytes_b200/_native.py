@@ -15,6 +15,7 @@ LIB_PATH = os.path.join(_HERE, "lib", "libmpsbnb_b200.so")
 HEADER_PATH = os.path.join(_HERE, "..", "include", "mpsbnb_b200.h")
 
 F16, BF16, F32 = 0, 1, 2
+GROUP_PDL = 1
 NF4, FP4 = 0, 1
 _DT = {torch.float16: F16, torch.bfloat16: BF16, torch.float32: F32}
 _QT = {"nf4": NF4, "fp4": FP4}
@@ -32,7 +33,7 @@ class Linear4Desc(C.Structure):
 class GroupPlan(C.Structure):
     """mpsbnb_group_plan of include/mpsbnb_b200.h."""
     _fields_ = [("dev", C.c_void_p), ("units_offset", C.c_int64), ("n_linears", C.c_int), ("n_units", C.c_int),
-                ("M", C.c_int), ("x_dtype", C.c_int), ("quant_type", C.c_int), ("reserved", C.c_int)]
+                ("M", C.c_int), ("x_dtype", C.c_int), ("quant_type", C.c_int), ("flags", C.c_int)]
 
 
 class NativeLibraryError(RuntimeError):

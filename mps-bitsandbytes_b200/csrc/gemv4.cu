@@ -26,6 +26,9 @@
 // the one resource (shared-memory bandwidth) that is already the tightest.
 #include "common.cuh"
 #include "ops.cuh"
+#include "sm100.cuh"
+
+#include <string.h>
 
 namespace mpsbnb {
 
@@ -325,6 +328,8 @@ __global__ void stack_expand_kernel(const T *__restrict__ G, int g, int M, int H
 // projections were accumulated into one fp32 matrix, and re-arms the accumulator.
 template <typename T>
 __global__ void stack_boundary_acc_kernel(float *__restrict__ acc, float alpha, int64_t n, T *__restrict__ h) {
+    sm100::pdl_launch_dependents();
+    sm100::pdl_grid_dependency_wait();
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
         h[i] = from_f32<T>(alpha * acc[i]);
         acc[i] = 0.0f;
@@ -335,16 +340,24 @@ __global__ void stack_boundary_acc_kernel(float *__restrict__ acc, float alpha, 
 
 using namespace mpsbnb;
 
-extern "C" int mpsbnb_stack_boundary_acc(float *acc, float alpha, int64_t n, void *h, int dtype, void *stream) {
+extern "C" int mpsbnb_stack_boundary_acc(float *acc, float alpha, int64_t n, void *h, int dtype, int flags,
+                                         void *stream) {
     if (!is_16bit(dtype) || n < 0) return MPSBNB_ERR_INVALID_ARG;
     if (n == 0) return MPSBNB_OK;
     if (acc == nullptr || h == nullptr) return MPSBNB_ERR_INVALID_ARG;
     int64_t grid = (n + 255) / 256;
     if (grid > sm_count() * 8) grid = sm_count() * 8;
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3((unsigned)grid); cfg.blockDim = dim3(256); cfg.stream = (cudaStream_t)stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = (flags & MPSBNB_GROUP_PDL) ? 1 : 0;
     if (dtype == MPSBNB_F16)
-        stack_boundary_acc_kernel<__half><<<(int)grid, 256, 0, (cudaStream_t)stream>>>(acc, alpha, n, (__half *)h);
+        MPSBNB_CUDA_TRY(cudaLaunchKernelEx(&cfg, stack_boundary_acc_kernel<__half>, acc, alpha, n, (__half *)h));
     else
-        stack_boundary_acc_kernel<__nv_bfloat16><<<(int)grid, 256, 0, (cudaStream_t)stream>>>(acc, alpha, n, (__nv_bfloat16 *)h);
+        MPSBNB_CUDA_TRY(cudaLaunchKernelEx(&cfg, stack_boundary_acc_kernel<__nv_bfloat16>, acc, alpha, n, (__nv_bfloat16 *)h));
     return check_launch();
 }
 

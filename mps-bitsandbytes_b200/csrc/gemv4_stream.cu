@@ -4,23 +4,23 @@
 // analogue is nf4_matmul_simd, mps_bitsandbytes.mm:440-560, launched once per linear).
 //
 // Bound: HBM.  Every packed byte crosses the memory system once.  One persistent CTA per SM
-// with 21 warps:
+// with 22 warps:
 //   warp 16  TMA producer.  Work is cut into units of 32 weight rows x a run of stages; a
 //            stage is 32 rows x 1024 k = 16 KB of packed bytes, fetched as four
 //            cp.async.bulk.tensor boxes (32 rows x 128 B, 128-byte swizzle) into a ring of
 //            shared-memory slots.  The ring keeps 100+ KB in flight per SM regardless of what the
 //            consumers are doing (register prefetch could not: it was the limiter before).
-//   warps 17-19  loaders, taking stages in turn.  For its stage a loader writes, into the same
+//   warps 17-20  loaders, taking stages in turn.  For its stage a loader writes, into the same
 //            slot, the 32 x 16 block scales already expanded to fp32 (double-quantised absmax is
 //            int8 * absmax2 / 127) and the 1024 x values of each batch row, so consumers never
-//            touch global memory.  Three of them keep three stages' worth of loads in flight.
+//            touch global memory.  Four of them keep four stages' worth of loads in flight.
 //   warps 0-15  consumers.  Warp (rt, kg) owns row tile rt (16 rows) and blocks 2 kg, 2 kg + 1
 //            of every stage.  Per block: two 8-byte shared loads (rows g and g + 8 — the swizzle
 //            and a row permutation make them bank-conflict free), 16 table lookups that turn a
 //            packed byte into a pair of 16-bit codes (one byte-permute + one shared load each,
 //            table replicated per lane), 4 mma.sync.m16n8k16 with the weights as the M side,
 //            then one fp32 multiply-add per row with the block scale.
-//   warp 20  reducer.  At the end of a unit every consumer warp drops its partial sums into a
+//   warp 21  reducer.  At the end of a unit every consumer warp drops its partial sums into a
 //            double-buffered shared array and signals an mbarrier; the reducer adds the eight kg
 //            partials of each row and stores them (or atomically adds them to an fp32
 //            accumulator when K is split across units or several linears sum into one output).
@@ -39,7 +39,7 @@ namespace mpsbnb {
 using namespace sm100;
 
 constexpr int SG_CONSUMERS = 16;
-constexpr int SG_LOADERS = 3;
+constexpr int SG_LOADERS = 4;                           // must equal SG_MAX_XS (see there)
 constexpr int SG_THREADS = (SG_CONSUMERS + 1 + SG_LOADERS + 1) * 32;   // + TMA warp + reducer warp
 constexpr int SG_ROWS = 32;                              // weight rows per unit
 constexpr int SG_STAGE_BLOCKS = 16;                      // quantisation blocks (of 64 k) per stage
@@ -48,12 +48,18 @@ constexpr int SG_A_BYTES = SG_STAGE_BLOCKS * SG_ROWS * 4;    // 2048: fp32 scale
 constexpr int SG_XPITCH = 2048 + 64;                     // bytes between batch rows of x in a slot
 constexpr int SG_RED_BYTES = SG_CONSUMERS * 8 * 20 * 4;  // [warp][m][16 rows + 4 pad] fp32
 constexpr int SG_MAX_SLOTS = 8;
-constexpr int SG_L2_AHEAD = 16;                         // stages pulled into L2 ahead of the ring
 constexpr int SG_MAX_M = 8;
 
 // status word of this translation unit (device code is not linked relocatably); read by
 // stream_status_fetch() on behalf of mpsbnb_device_status()
 static __device__ int g_stream_status = 0;
+#ifdef MPSBNB_PROF
+static __device__ long long g_prof[148 * 16 * 4];
+#define PROF_T(v) const long long v = clock64()
+#else
+#define PROF_T(v)
+#endif
+
 
 struct StreamLinear {
     CUtensorMap map;          // packed weights as [N][row_bytes] bytes; box 128 B x 32 rows, 128-byte swizzle
@@ -69,6 +75,8 @@ struct StreamLinear {
     int y_dtype;
     int x_vec_ok;             // 16-byte loads of x are legal
     int x_bulk_ok;            // every stage's x columns are one 16-byte-aligned contiguous run: TMA bulk copies
+    int map3d;                // map is {128 B, N rows, row_bytes / 128}: one box {128, 32, 4} fetches a whole stage
+    int pad_;
 };
 
 struct StreamUnit { int lin, row0, s_begin, s_end; };
@@ -76,8 +84,7 @@ struct StreamUnit { int lin, row0, s_begin, s_end; };
 struct StreamArgs {
     const StreamLinear *lins; // device array, or nullptr: use `one`
     const StreamUnit *units;  // device array, or nullptr: unit u = rows [32 u, 32 u + 32) x all stages of `one`
-    int nunits, M, quant_type, nslots, slot_bytes;
-    int debug;                // DEBUGVAR
+    int nunits, M, quant_type;
     uint32_t zero;            // always 0; known only at run time (orders the slot release after the loads)
     StreamLinear one;
 };
@@ -99,139 +106,151 @@ template <> __device__ __forceinline__ uint32_t pair_bits<__half>(float lo, floa
 template <> __device__ __forceinline__ uint32_t pair_bits<__nv_bfloat16>(float lo, float hi) { const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi); return *reinterpret_cast<const uint32_t *>(&h); }
 
 // ---- shared-memory access by 32-bit shared address (no generic-pointer arithmetic in the hot loop)
-template <int OFF> __device__ __forceinline__ uint2 lds64(uint32_t addr) {
-    uint2 v;
-    asm volatile("ld.shared.v2.u32 {%0, %1}, [%2+%3];" : "=r"(v.x), "=r"(v.y) : "r"(addr), "n"(OFF));
-    return v;
-}
-template <int OFF> __device__ __forceinline__ uint4 lds128(uint32_t addr) {
-    uint4 v;
-    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4+%5];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr), "n"(OFF));
-    return v;
-}
-template <int OFF> __device__ __forceinline__ float lds_f32(uint32_t addr) {
-    float v;
-    asm volatile("ld.shared.f32 %0, [%1+%2];" : "=f"(v) : "r"(addr), "n"(OFF));
-    return v;
-}
-__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
-    uint32_t v;
-    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
-    return v;
-}
 __device__ __forceinline__ void sts_f32(uint32_t addr, float v) { asm volatile("st.shared.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory"); }
 __device__ __forceinline__ void sts32(uint32_t addr, uint32_t v) { asm volatile("st.shared.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory"); }
 __device__ __forceinline__ void sts128(uint32_t addr, uint4 v) {
     asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
 
-// d = a * b + c  (m16n8k16, fp32 accumulate)
-template <typename XT> __device__ __forceinline__ void mma_abc(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1, const float (&c)[4]);
-template <> __device__ __forceinline__ void mma_abc<__half>(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1, const float (&c)[4]) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
-                 : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
-                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(c[0]), "f"(c[1]), "f"(c[2]), "f"(c[3]));
-}
-template <> __device__ __forceinline__ void mma_abc<__nv_bfloat16>(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1, const float (&c)[4]) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
-                 : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
-                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(c[0]), "f"(c[1]), "f"(c[2]), "f"(c[3]));
-}
-
-// A consumer warp's work on one quantisation block (16 weight rows x 64 k) is written in PTX so
-// that the instruction stream is exactly what the design counts on.
-// fetch_block: 3 address adds and 6 shared loads bring the block's operands into registers —
-//   8 packed bytes of row g and of row g + 8, the two block scales, and 16 x values (the x
-//   registers stay zero in lanes that have no batch row).  After it the slot is no longer needed.
-__device__ __forceinline__ void fetch_block(uint32_t (&w)[4], float (&am)[2], uint32_t (&xr)[8], uint32_t sb,
-                                            uint32_t woff, uint32_t aoff, uint32_t xoff, uint32_t hasx) {
+// A consumer warp's inner loop is written in PTX so that the instruction stream is what the design
+// counts on.  Per stage a warp owns two quantisation blocks (16 weight rows x 64 k each).
+//
+// fetch_stage: four 8-byte shared loads bring the packed bytes of both blocks into registers
+//   (w[0..1]: block 0 row g, w[2..3]: block 0 row g + 8, w[4..7]: block 1).  After it the weight
+//   slot is no longer needed by this warp.
+__device__ __forceinline__ void fetch_stage(uint32_t (&w)[8], uint32_t wa0, uint32_t wa1) {
     asm volatile(
-        "{\n\t"
-        ".reg .b32 aw, aa, ax;\n\t"
-        ".reg .pred p;\n\t"
-        "setp.ne.u32 p, %18, 0;\n\t"
-        "add.u32 aw, %14, %15;\n\t"
-        "add.u32 aa, %14, %16;\n\t"
-        "add.u32 ax, %14, %17;\n\t"
-        "ld.shared.v2.u32 {%0, %1}, [aw];\n\t"
-        "ld.shared.v2.u32 {%2, %3}, [aw+1024];\n\t"
-        "@p ld.shared.v4.u32 {%6, %7, %8, %9}, [ax];\n\t"
-        "@p ld.shared.v4.u32 {%10, %11, %12, %13}, [ax+16];\n\t"
-        "ld.shared.f32 %4, [aa];\n\t"
-        "ld.shared.f32 %5, [aa+32];\n\t"
-        "}\n"
-        : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]), "=f"(am[0]), "=f"(am[1]), "+r"(xr[0]), "+r"(xr[1]),
-          "+r"(xr[2]), "+r"(xr[3]), "+r"(xr[4]), "+r"(xr[5]), "+r"(xr[6]), "+r"(xr[7])
-        : "r"(sb), "r"(woff), "r"(aoff), "r"(xoff), "r"(hasx)
+        "ld.shared.v2.u32 {%0, %1}, [%8];\n\t"
+        "ld.shared.v2.u32 {%2, %3}, [%8+1024];\n\t"
+        "ld.shared.v2.u32 {%4, %5}, [%9];\n\t"
+        "ld.shared.v2.u32 {%6, %7}, [%9+1024];\n\t"
+        : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]), "=r"(w[4]), "=r"(w[5]), "=r"(w[6]), "=r"(w[7])
+        : "r"(wa0), "r"(wa1)
         : "memory");
 }
 
-// compute_block: 16 x (byte-permute, table load) turn the packed bytes into MMA A fragments
-//   (w[0], w[1]: row g; w[2], w[3]: row g + 8), 4 MMAs contract them with x, and 4 FMAs apply the
-//   two block scales.  lw is the lane word of the table address.
-#define MPSBNB_COMPUTE_ASM(TYPE)                                                                            \
+// Sixteen (byte-permute, table load) pairs: packed bytes of rows g (wa, wb) and g + 8 (wc, wd) become
+// the A fragments F0..F15 of four MMAs.  LW is the lane word of the table address.
+#define MPSBNB_LUT16(F, WA, WB, WC, WD, LW)                                                    \
+    "prmt.b32 ad, " WA ", " LW ", 0x7604;\n\t ld.shared.u32 " F "0, [ad];\n\t"                   \
+    "prmt.b32 ad, " WC ", " LW ", 0x7604;\n\t ld.shared.u32 " F "1, [ad];\n\t"                   \
+    "prmt.b32 ad, " WA ", " LW ", 0x7614;\n\t ld.shared.u32 " F "2, [ad];\n\t"                   \
+    "prmt.b32 ad, " WC ", " LW ", 0x7614;\n\t ld.shared.u32 " F "3, [ad];\n\t"                   \
+    "prmt.b32 ad, " WA ", " LW ", 0x7624;\n\t ld.shared.u32 " F "4, [ad];\n\t"                   \
+    "prmt.b32 ad, " WC ", " LW ", 0x7624;\n\t ld.shared.u32 " F "5, [ad];\n\t"                   \
+    "prmt.b32 ad, " WA ", " LW ", 0x7634;\n\t ld.shared.u32 " F "6, [ad];\n\t"                   \
+    "prmt.b32 ad, " WC ", " LW ", 0x7634;\n\t ld.shared.u32 " F "7, [ad];\n\t"                   \
+    "prmt.b32 ad, " WB ", " LW ", 0x7604;\n\t ld.shared.u32 " F "8, [ad];\n\t"                   \
+    "prmt.b32 ad, " WD ", " LW ", 0x7604;\n\t ld.shared.u32 " F "9, [ad];\n\t"                   \
+    "prmt.b32 ad, " WB ", " LW ", 0x7614;\n\t ld.shared.u32 " F "10, [ad];\n\t"                  \
+    "prmt.b32 ad, " WD ", " LW ", 0x7614;\n\t ld.shared.u32 " F "11, [ad];\n\t"                  \
+    "prmt.b32 ad, " WB ", " LW ", 0x7624;\n\t ld.shared.u32 " F "12, [ad];\n\t"                  \
+    "prmt.b32 ad, " WD ", " LW ", 0x7624;\n\t ld.shared.u32 " F "13, [ad];\n\t"                  \
+    "prmt.b32 ad, " WB ", " LW ", 0x7634;\n\t ld.shared.u32 " F "14, [ad];\n\t"                  \
+    "prmt.b32 ad, " WD ", " LW ", 0x7634;\n\t ld.shared.u32 " F "15, [ad];\n\t"
+
+#define MPSBNB_MMA(TYPE, D, A0, A1, A2, A3, B0, B1, C)                                         \
+    "mma.sync.aligned.m16n8k16.row.col.f32." TYPE "." TYPE ".f32 {" D "0," D "1," D "2," D "3}, {" A0 "," A1 "," A2 "," A3 "}, {" B0 "," B1 "}, " C ";\n\t"
+
+// compute_stage: both blocks of a stage.  x (16 values per block; lanes without a batch row read a
+// zero area) and the four block scales come from the scale/x slot at xa0, xa1, aa0, aa1; the 32 table
+// loads of both blocks are issued before the first MMA, the two MMA chains are interleaved, and eight
+// FMAs apply the scales.  The weight registers were filled by fetch_stage one iteration earlier.
+#define MPSBNB_STAGE_ASM(TYPE)                                                                              \
     asm volatile(                                                                                           \
         "{\n\t"                                                                                             \
-        ".reg .b32 ad;\n\t"                                                                                 \
-        ".reg .b32 f<16>;\n\t"                                                                              \
-        ".reg .f32 t<4>, z;\n\t"                                                                            \
+        ".reg .b32 ad, x<8>, y<8>;\n\t"                                                                     \
+        ".reg .b32 f<16>, g<16>;\n\t"                                                                       \
+        ".reg .f32 m<4>, t<4>, u<4>, z;\n\t"                                                                \
+        "ld.shared.v4.u32 {x0, x1, x2, x3}, [%14];\n\t"                                                     \
+        "ld.shared.v4.u32 {x4, x5, x6, x7}, [%14+16];\n\t"                                                  \
+        "ld.shared.v4.u32 {y0, y1, y2, y3}, [%15];\n\t"                                                     \
+        "ld.shared.v4.u32 {y4, y5, y6, y7}, [%15+16];\n\t"                                                  \
+        "ld.shared.f32 m0, [%12];\n\t"                                                                      \
+        "ld.shared.f32 m1, [%12+32];\n\t"                                                                   \
+        "ld.shared.f32 m2, [%13];\n\t"                                                                      \
+        "ld.shared.f32 m3, [%13+32];\n\t"                                                                   \
         "mov.f32 z, 0f00000000;\n\t"                                                                        \
-        "prmt.b32 ad, %4, %18, 0x7604;\n\t ld.shared.u32 f0, [ad];\n\t"                                     \
-        "prmt.b32 ad, %6, %18, 0x7604;\n\t ld.shared.u32 f1, [ad];\n\t"                                     \
-        "prmt.b32 ad, %4, %18, 0x7614;\n\t ld.shared.u32 f2, [ad];\n\t"                                     \
-        "prmt.b32 ad, %6, %18, 0x7614;\n\t ld.shared.u32 f3, [ad];\n\t"                                     \
-        "prmt.b32 ad, %4, %18, 0x7624;\n\t ld.shared.u32 f4, [ad];\n\t"                                     \
-        "prmt.b32 ad, %6, %18, 0x7624;\n\t ld.shared.u32 f5, [ad];\n\t"                                     \
-        "prmt.b32 ad, %4, %18, 0x7634;\n\t ld.shared.u32 f6, [ad];\n\t"                                     \
-        "prmt.b32 ad, %6, %18, 0x7634;\n\t ld.shared.u32 f7, [ad];\n\t"                                     \
-        "prmt.b32 ad, %5, %18, 0x7604;\n\t ld.shared.u32 f8, [ad];\n\t"                                     \
-        "prmt.b32 ad, %7, %18, 0x7604;\n\t ld.shared.u32 f9, [ad];\n\t"                                     \
-        "prmt.b32 ad, %5, %18, 0x7614;\n\t ld.shared.u32 f10, [ad];\n\t"                                    \
-        "prmt.b32 ad, %7, %18, 0x7614;\n\t ld.shared.u32 f11, [ad];\n\t"                                    \
-        "prmt.b32 ad, %5, %18, 0x7624;\n\t ld.shared.u32 f12, [ad];\n\t"                                    \
-        "prmt.b32 ad, %7, %18, 0x7624;\n\t ld.shared.u32 f13, [ad];\n\t"                                    \
-        "prmt.b32 ad, %5, %18, 0x7634;\n\t ld.shared.u32 f14, [ad];\n\t"                                    \
-        "prmt.b32 ad, %7, %18, 0x7634;\n\t ld.shared.u32 f15, [ad];\n\t"                                    \
-        "mma.sync.aligned.m16n8k16.row.col.f32." TYPE "." TYPE ".f32 {t0,t1,t2,t3}, {f0,f1,f2,f3}, {%10,%11}, {z,z,z,z};\n\t"        \
-        "mma.sync.aligned.m16n8k16.row.col.f32." TYPE "." TYPE ".f32 {t0,t1,t2,t3}, {f4,f5,f6,f7}, {%12,%13}, {t0,t1,t2,t3};\n\t"    \
-        "mma.sync.aligned.m16n8k16.row.col.f32." TYPE "." TYPE ".f32 {t0,t1,t2,t3}, {f8,f9,f10,f11}, {%14,%15}, {t0,t1,t2,t3};\n\t"  \
-        "mma.sync.aligned.m16n8k16.row.col.f32." TYPE "." TYPE ".f32 {t0,t1,t2,t3}, {f12,f13,f14,f15}, {%16,%17}, {t0,t1,t2,t3};\n\t" \
-        "fma.rn.f32 %0, %8, t0, %0;\n\t"                                                                    \
-        "fma.rn.f32 %1, %8, t1, %1;\n\t"                                                                    \
-        "fma.rn.f32 %2, %9, t2, %2;\n\t"                                                                    \
-        "fma.rn.f32 %3, %9, t3, %3;\n\t"                                                                    \
+        MPSBNB_LUT16("f", "%4", "%5", "%6", "%7", "%16")                                                    \
+        MPSBNB_LUT16("g", "%8", "%9", "%10", "%11", "%16")                                                  \
+        MPSBNB_MMA(TYPE, "t", "f0", "f1", "f2", "f3", "x0", "x1", "{z,z,z,z}")                              \
+        MPSBNB_MMA(TYPE, "u", "g0", "g1", "g2", "g3", "y0", "y1", "{z,z,z,z}")                              \
+        MPSBNB_MMA(TYPE, "t", "f4", "f5", "f6", "f7", "x2", "x3", "{t0,t1,t2,t3}")                          \
+        MPSBNB_MMA(TYPE, "u", "g4", "g5", "g6", "g7", "y2", "y3", "{u0,u1,u2,u3}")                          \
+        MPSBNB_MMA(TYPE, "t", "f8", "f9", "f10", "f11", "x4", "x5", "{t0,t1,t2,t3}")                        \
+        MPSBNB_MMA(TYPE, "u", "g8", "g9", "g10", "g11", "y4", "y5", "{u0,u1,u2,u3}")                        \
+        MPSBNB_MMA(TYPE, "t", "f12", "f13", "f14", "f15", "x6", "x7", "{t0,t1,t2,t3}")                      \
+        MPSBNB_MMA(TYPE, "u", "g12", "g13", "g14", "g15", "y6", "y7", "{u0,u1,u2,u3}")                      \
+        "fma.rn.f32 %0, m0, t0, %0;\n\t fma.rn.f32 %1, m0, t1, %1;\n\t"                                     \
+        "fma.rn.f32 %2, m1, t2, %2;\n\t fma.rn.f32 %3, m1, t3, %3;\n\t"                                     \
+        "fma.rn.f32 %0, m2, u0, %0;\n\t fma.rn.f32 %1, m2, u1, %1;\n\t"                                     \
+        "fma.rn.f32 %2, m3, u2, %2;\n\t fma.rn.f32 %3, m3, u3, %3;\n\t"                                     \
         "}\n"                                                                                               \
         : "+f"(acc[0]), "+f"(acc[1]), "+f"(acc[2]), "+f"(acc[3])                                            \
-        : "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]), "f"(am[0]), "f"(am[1]), "r"(xr[0]), "r"(xr[1]),       \
-          "r"(xr[2]), "r"(xr[3]), "r"(xr[4]), "r"(xr[5]), "r"(xr[6]), "r"(xr[7]), "r"(lw))
+        : "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]),           \
+          "r"(aa0), "r"(aa1), "r"(xa0), "r"(xa1), "r"(lw)                                                   \
+        : "memory")
 
-template <typename XT>
-__device__ __forceinline__ void compute_block(float (&acc)[4], const uint32_t (&w)[4], const float (&am)[2],
-                                              const uint32_t (&xr)[8], uint32_t lw);
-template <>
-__device__ __forceinline__ void compute_block<__half>(float (&acc)[4], const uint32_t (&w)[4], const float (&am)[2],
-                                                      const uint32_t (&xr)[8], uint32_t lw) {
-    MPSBNB_COMPUTE_ASM("f16");
-}
-template <>
-__device__ __forceinline__ void compute_block<__nv_bfloat16>(float (&acc)[4], const uint32_t (&w)[4], const float (&am)[2],
-                                                             const uint32_t (&xr)[8], uint32_t lw) {
-    MPSBNB_COMPUTE_ASM("bf16");
-}
+// compute_block: one block only (the ragged last stage of a row whose K is not a multiple of 128)
+#define MPSBNB_BLOCK_ASM(TYPE)                                                                              \
+    asm volatile(                                                                                           \
+        "{\n\t"                                                                                             \
+        ".reg .b32 ad, x<8>;\n\t"                                                                           \
+        ".reg .b32 f<16>;\n\t"                                                                              \
+        ".reg .f32 m<2>, t<4>, z;\n\t"                                                                      \
+        "ld.shared.v4.u32 {x0, x1, x2, x3}, [%9];\n\t"                                                      \
+        "ld.shared.v4.u32 {x4, x5, x6, x7}, [%9+16];\n\t"                                                   \
+        "ld.shared.f32 m0, [%8];\n\t"                                                                       \
+        "ld.shared.f32 m1, [%8+32];\n\t"                                                                    \
+        "mov.f32 z, 0f00000000;\n\t"                                                                        \
+        MPSBNB_LUT16("f", "%4", "%5", "%6", "%7", "%10")                                                    \
+        MPSBNB_MMA(TYPE, "t", "f0", "f1", "f2", "f3", "x0", "x1", "{z,z,z,z}")                              \
+        MPSBNB_MMA(TYPE, "t", "f4", "f5", "f6", "f7", "x2", "x3", "{t0,t1,t2,t3}")                          \
+        MPSBNB_MMA(TYPE, "t", "f8", "f9", "f10", "f11", "x4", "x5", "{t0,t1,t2,t3}")                        \
+        MPSBNB_MMA(TYPE, "t", "f12", "f13", "f14", "f15", "x6", "x7", "{t0,t1,t2,t3}")                      \
+        "fma.rn.f32 %0, m0, t0, %0;\n\t fma.rn.f32 %1, m0, t1, %1;\n\t"                                     \
+        "fma.rn.f32 %2, m1, t2, %2;\n\t fma.rn.f32 %3, m1, t3, %3;\n\t"                                     \
+        "}\n"                                                                                               \
+        : "+f"(acc[0]), "+f"(acc[1]), "+f"(acc[2]), "+f"(acc[3])                                            \
+        : "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(aa0), "r"(xa0), "r"(lw)                           \
+        : "memory")
+
+template <typename XT> struct StageOps;
+template <> struct StageOps<__half> {
+    static __device__ __forceinline__ void stage(float (&acc)[4], const uint32_t (&w)[8], uint32_t aa0, uint32_t aa1,
+                                                 uint32_t xa0, uint32_t xa1, uint32_t lw) { MPSBNB_STAGE_ASM("f16"); }
+    static __device__ __forceinline__ void block(float (&acc)[4], const uint32_t (&w)[8], uint32_t aa0, uint32_t xa0,
+                                                 uint32_t lw) { MPSBNB_BLOCK_ASM("f16"); }
+};
+template <> struct StageOps<__nv_bfloat16> {
+    static __device__ __forceinline__ void stage(float (&acc)[4], const uint32_t (&w)[8], uint32_t aa0, uint32_t aa1,
+                                                 uint32_t xa0, uint32_t xa1, uint32_t lw) { MPSBNB_STAGE_ASM("bf16"); }
+    static __device__ __forceinline__ void block(float (&acc)[4], const uint32_t (&w)[8], uint32_t aa0, uint32_t xa0,
+                                                 uint32_t lw) { MPSBNB_BLOCK_ASM("bf16"); }
+};
 
 // Shared-memory map, in ABSOLUTE shared-window addresses.  The code-pair table sits at exactly
 // 128 KiB so that "table + byte * 256 + lane * 4" is one byte-permute of (weight word, lane word):
 // byte 0 = lane * 4, byte 1 = the weight byte, byte 2 = 0x02 — no addition.  Below it: partial
-// sums, barriers and most ring slots; above it (from 192 KiB) one more slot.
+// sums, barriers, the scale/x ring and most weight slots; above it (from 192 KiB) two more slots.
 constexpr uint32_t SG_LUT_ABS = 131072u;
 constexpr uint32_t SG_HIGH_ABS = 196608u;
 constexpr int SG_SMEM_BYTES = 227 * 1024;
+constexpr int SG_MAX_XS = 8;
+// Stage i is filled by loader warp i % SG_LOADERS into scale/x slot i % SG_MAX_XS.  An mbarrier parity
+// wait only distinguishes "this phase" from "the one before", so every waiter has to see EVERY phase
+// of a barrier: all fills of one slot must come from the same warp, one after the other.  With as many
+// the slot count a multiple of the loader count, the slot determines the loader.  (Two warps filling the same slot in
+// different rounds could pass the same parity test early and arrive twice in one phase.)
+// The ring has 8 slots for batch <= 2 and 4 above; both are multiples of the number of loaders, so
+// slot i % nxs is always filled by warp (i % nxs) % SG_LOADERS.
+static_assert(SG_MAX_XS % SG_LOADERS == 0 && 4 % SG_LOADERS == 0, "each scale/x slot must belong to exactly one loader warp");
 
 struct SlotMap {
-    uint32_t low0, high0, bytes;
+    uint32_t low0, high0;
     int nlow, nslots;
     __device__ __forceinline__ uint32_t addr(int slot) const {
-        return slot < nlow ? low0 + (uint32_t)slot * bytes : high0 + (uint32_t)(slot - nlow) * bytes;
+        return slot < nlow ? low0 + (uint32_t)slot * SG_W_BYTES : high0 + (uint32_t)(slot - nlow) * SG_W_BYTES;
     }
 };
 
@@ -240,31 +259,39 @@ __global__ void __launch_bounds__(SG_THREADS, 1) gemv4_stream_kernel(const __gri
     extern __shared__ __align__(1024) unsigned char smem[];
     const uint32_t s_base = smem_u32(smem);
     const uint32_t s_red = s_base;                                   // 2 x SG_RED_BYTES
-    const uint32_t s_bar = s_base + 2 * SG_RED_BYTES;                // full[8], empty[8], red_full[2], red_empty[2], flag
+    // full[8] empty[8] red_full[2] red_empty[2] xfull[8] xempty[8] (288 B), abort flag, 32 zero bytes at +320
+    const uint32_t s_bar = s_base + 2 * SG_RED_BYTES;
+    const uint32_t s_zero = s_bar + 320u;
+    const int nxs = a.M <= 2 ? SG_MAX_XS : 4;                        // scale/x slots (released after the MMAs)
+    const uint32_t xs_bytes = (uint32_t)(SG_A_BYTES + ((a.M * SG_XPITCH + 127) / 128) * 128);
+    const uint32_t s_xs = (s_bar + 384u + 127u) & ~127u;
     SlotMap sm;
-    sm.bytes = (uint32_t)a.slot_bytes;
-    sm.low0 = (s_bar + 256u + 1023u) & ~1023u;
+    sm.low0 = (s_xs + (uint32_t)nxs * xs_bytes + 1023u) & ~1023u;
     sm.high0 = SG_HIGH_ABS;
-    sm.nlow = (int)((SG_LUT_ABS - sm.low0) / sm.bytes);
+    sm.nlow = (int)((SG_LUT_ABS - sm.low0) / SG_W_BYTES);
     {
-        const int nhigh = (int)((s_base + (uint32_t)SG_SMEM_BYTES - SG_HIGH_ABS) / sm.bytes);
-        int n = sm.nlow + nhigh;
+        const int nhigh = (int)((s_base + (uint32_t)SG_SMEM_BYTES - SG_HIGH_ABS) / SG_W_BYTES);
+        const int n = sm.nlow + nhigh;
         sm.nslots = n > SG_MAX_SLOTS ? SG_MAX_SLOTS : n;
         if (sm.nlow > sm.nslots) sm.nlow = sm.nslots;
     }
     const int nslots = sm.nslots;
     unsigned char *p_generic0 = smem - s_base;                       // generic pointer of shared address 0
-    volatile uint32_t *abort_flag = reinterpret_cast<volatile uint32_t *>(p_generic0 + s_bar + (2 * SG_MAX_SLOTS + 4) * 8);
+    volatile uint32_t *abort_flag = reinterpret_cast<volatile uint32_t *>(p_generic0 + s_bar + 8 * (2 * SG_MAX_SLOTS + 4 + 2 * SG_MAX_XS));
     auto full_bar = [&](int s) { return s_bar + 8u * s; };
     auto empty_bar = [&](int s) { return s_bar + 8u * (SG_MAX_SLOTS + s); };
     auto red_full = [&](int b) { return s_bar + 8u * (2 * SG_MAX_SLOTS + b); };
     auto red_empty = [&](int b) { return s_bar + 8u * (2 * SG_MAX_SLOTS + 2 + b); };
+    auto xfull_bar = [&](int s) { return s_bar + 8u * (2 * SG_MAX_SLOTS + 4 + s); };
+    auto xempty_bar = [&](int s) { return s_bar + 8u * (2 * SG_MAX_SLOTS + 4 + SG_MAX_XS + s); };
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    pdl_launch_dependents();
 
     if (tid == 0) {
-        for (int s = 0; s < nslots; ++s) { mbar_init(full_bar(s), (a.debug & 2) ? 1 : 2); mbar_init(empty_bar(s), SG_CONSUMERS); }
+        for (int s = 0; s < nslots; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), SG_CONSUMERS); }
         for (int b = 0; b < 2; ++b) { mbar_init(red_full(b), SG_CONSUMERS); mbar_init(red_empty(b), 1); }
+        for (int s = 0; s < nxs; ++s) { mbar_init(xfull_bar(s), 1); mbar_init(xempty_bar(s), SG_CONSUMERS); }
         *abort_flag = 0;
         fence_mbar_init();
     }
@@ -280,11 +307,11 @@ __global__ void __launch_bounds__(SG_THREADS, 1) gemv4_stream_kernel(const __gri
         for (int j = 0; j < 32; ++j)
             sts32(SG_LUT_ABS + (uint32_t)((warp * 32 + j) * 256 + lane * 4), __shfl_sync(0xffffffffu, mine, j));
     } else {
-        // x areas start as zeros: columns beyond K are never written, and 0 * (stale bits) must be 0
-        const int xbytes = (int)sm.bytes - SG_W_BYTES - SG_A_BYTES;
-        for (int s = 0; s < nslots; ++s)
-            for (int o = (tid - 256) * 16; o < xbytes; o += (SG_THREADS - 256) * 16)
-                sts128(sm.addr(s) + SG_W_BYTES + SG_A_BYTES + o, make_uint4(0u, 0u, 0u, 0u));
+        // the scale/x ring starts as zeros (x columns beyond K are never written, and 0 * stale bits must
+        // be 0), and so does the zero area that lanes without a batch row read their x from
+        const int total = nxs * (int)xs_bytes;
+        for (int o = (tid - 256) * 16; o < total; o += (SG_THREADS - 256) * 16) sts128(s_xs + o, make_uint4(0u, 0u, 0u, 0u));
+        if (tid == 256) { sts128(s_zero, make_uint4(0u, 0u, 0u, 0u)); sts128(s_zero + 16, make_uint4(0u, 0u, 0u, 0u)); }
     }
     fence_proxy_async_smem();
     __syncthreads();
@@ -298,53 +325,39 @@ __global__ void __launch_bounds__(SG_THREADS, 1) gemv4_stream_kernel(const __gri
     auto lin_of = [&](int i) -> const StreamLinear * { return a.lins != nullptr ? a.lins + i : &a.one; };
 
     if (warp == SG_CONSUMERS) {
-        // ------------------------------------------------------------ TMA producer: packed weights, and x
+        // ------------------------------------------------------------ TMA producer: packed weights
         if (lane == 0) {
-            // A second cursor runs SG_L2_AHEAD stages in front and pulls those boxes into L2, so the
-            // loads into the (small) shared-memory ring see L2 latency, not HBM latency.
-            int pu = blockIdx.x, ps = 0, ps_end = 0, prow0 = 0;
-            const StreamLinear *pL = nullptr;
-            bool phave = false;
-            auto prefetch_one = [&]() {
-                for (;;) {
-                    if (!phave) {
-                        if (pu >= a.nunits) return;
-                        const StreamUnit pn = unit_of(pu);
-                        pL = lin_of(pn.lin); ps = pn.s_begin; ps_end = pn.s_end; prow0 = pn.row0; phave = true;
-                    }
-                    if (ps >= ps_end) { phave = false; pu += gridDim.x; continue; }
-#pragma unroll
-                    for (int p = 0; p < 4; ++p) tma_prefetch_l2_2d(&pL->map, (ps * 4 + p) * 128, prow0);
-                    ++ps;
-                    return;
-                }
-            };
-            if (a.debug & 4)
-                for (int i = 0; i < SG_L2_AHEAD; ++i) prefetch_one();
+            // The only serial thread on the data path: per stage one barrier wait, one expect-tx and one
+            // (3-D) tensor copy.  Weights never depend on the previous kernel in the stream, so this thread
+            // does not wait for it; the loaders, which bring x, do.
+            int u = blockIdx.x;
             int slot = 0; uint32_t ph = 0;
-            for (int u = blockIdx.x; u < a.nunits && !*abort_flag; u += gridDim.x) {
+            while (u < a.nunits && !*abort_flag) {
                 const StreamUnit un = unit_of(u);
                 const StreamLinear *L = lin_of(un.lin);
-                const unsigned char *xb = reinterpret_cast<const unsigned char *>(L->x);
-                for (int s = un.s_begin; s < un.s_end; ++s, slot = (slot + 1 == nslots ? 0 : slot + 1), ph ^= (slot == 0 ? 1u : 0u)) {
-                    if (a.debug & 4) prefetch_one();
-                    if (!mbar_wait_relaxed(empty_bar(slot), ph ^ 1u, abort_flag)) { atomicExch(&g_stream_status, 201); *abort_flag = 1; break; }
-                    const uint32_t dst = sm.addr(slot);
-                    const int k_base = s * (SG_STAGE_BLOCKS * 64);
-                    int xcols = L->K - k_base;                      // x columns of this stage (bulk copies need x_bulk_ok)
-                    xcols = xcols > SG_STAGE_BLOCKS * 64 ? SG_STAGE_BLOCKS * 64 : (xcols < 0 ? 0 : xcols);
-                    const uint32_t xbytes = L->x_bulk_ok ? (uint32_t)xcols * 2u : 0u;
-                    mbar_arrive_expect_tx(full_bar(slot), SG_W_BYTES + xbytes * (uint32_t)a.M);
-#pragma unroll
-                    for (int p = 0; p < 4; ++p)
-                        tma_load_2d(dst + p * 4096, &L->map, full_bar(slot), (s * 4 + p) * 128, un.row0);
-                    if (xbytes != 0u) {
-                        const int64_t col = k_base % L->x_period;
-                        for (int m = 0; m < a.M; ++m)
-                            bulk_load_1d(dst + SG_W_BYTES + SG_A_BYTES + m * SG_XPITCH, xb + ((int64_t)m * L->x_ld + col) * 2,
-                                         xbytes, full_bar(slot));
+                const CUtensorMap *map = &L->map;
+                const bool m3 = L->map3d != 0;
+                bool ok = true;
+                for (int s = un.s_begin; s < un.s_end; ++s) {
+                    if (!mbar_wait(empty_bar(slot), ph ^ 1u, abort_flag)) { atomicExch(&g_stream_status, 201); *abort_flag = 1; ok = false; break; }
+                    const uint32_t bar = full_bar(slot), dst = sm.addr(slot);
+#ifdef MPSBNB_SELFCHECK
+                    if ((dst & 1023u) || dst + SG_W_BYTES > s_base + SG_SMEM_BYTES || (dst < SG_LUT_ABS && dst + SG_W_BYTES > SG_LUT_ABS) ||
+                        dst < sm.low0 || un.row0 < 0 || un.row0 >= L->N || s < 0) {
+                        atomicExch(&g_stream_status, 304); *abort_flag = 1; ok = false; break;
                     }
+#endif
+                    mbar_arrive_expect_tx(bar, SG_W_BYTES);
+                    if (m3) {
+                        tma_load_3d(dst, map, bar, 0, un.row0, s * 4);
+                    } else {
+#pragma unroll
+                        for (int p = 0; p < 4; ++p) tma_load_2d(dst + p * 4096, map, bar, (s * 4 + p) * 128, un.row0);
+                    }
+                    if (++slot == nslots) { slot = 0; ph ^= 1u; }
                 }
+                if (!ok) break;
+                u += gridDim.x;
             }
         }
     } else if (warp == SG_CONSUMERS + 1 + SG_LOADERS) {
@@ -353,12 +366,13 @@ __global__ void __launch_bounds__(SG_THREADS, 1) gemv4_stream_kernel(const __gri
         const int rr = lane & 15, v = rr & 7;
         const int i = ((v >> 1) + 4 * (v & 1)) + 8 * (rr >> 3);
         const int wrt = lane >> 4;
+        pdl_grid_dependency_wait();                              // outputs may still be read by the previous kernel
         int uc = 0;
         for (int u = blockIdx.x; u < a.nunits && !*abort_flag; u += gridDim.x, ++uc) {
             const StreamUnit un = unit_of(u);
             const StreamLinear *L = lin_of(un.lin);
             const int buf = uc & 1;
-            if (!mbar_wait_relaxed(red_full(buf), (uint32_t)(uc >> 1) & 1u, abort_flag)) { atomicExch(&g_stream_status, 204); *abort_flag = 1; break; }
+            if (!mbar_wait(red_full(buf), (uint32_t)(uc >> 1) & 1u, abort_flag)) { atomicExch(&g_stream_status, 204); *abort_flag = 1; break; }
             const float *red = reinterpret_cast<const float *>(p_generic0 + s_red + buf * SG_RED_BYTES);
             const int n = un.row0 + lane;
             for (int m = 0; m < a.M; ++m) {
@@ -378,121 +392,149 @@ __global__ void __launch_bounds__(SG_THREADS, 1) gemv4_stream_kernel(const __gri
             if (lane == 0) mbar_arrive(red_empty(buf));
         }
     } else if (warp > SG_CONSUMERS) {
-        // ------------------------------------------------------------ loaders: block scales (and x when it cannot be bulk-copied)
-        // SG_LOADERS warps take stages in turn; each reads the scales of its NEXT stage before it
-        // stores the current one, so two rounds of global loads are in flight per warp.
+        // ------------------------------------------------------------ loaders: block scales and x into the scale/x ring
+        // SG_LOADERS warps take stages in turn; each reads the scales of its NEXT stage before it stores
+        // the current one, so two rounds of global loads are in flight per warp.
         const int me = warp - SG_CONSUMERS - 1;
-        if (a.debug & 2) return;   // DEBUGVAR
-        auto read_scales = [&](const StreamLinear *L, int row0, int s, float (&sc)[16]) {
-            const int n = row0 + lane;
-            const int b0 = s * SG_STAGE_BLOCKS;
-            const int64_t i0 = (int64_t)n * L->nb + b0;
-            if (n >= L->N) {
+        pdl_grid_dependency_wait();                              // x is written by the previous kernel in the stream
+        {
+            auto read_scales = [&](const StreamLinear *L, int row0, int s, float (&sc)[16]) {
+                const int n = row0 + lane;
+                const int b0 = s * SG_STAGE_BLOCKS;
+                const int64_t i0 = (int64_t)n * L->nb + b0;
+                if (n >= L->N) {
 #pragma unroll
-                for (int j = 0; j < 16; ++j) sc[j] = 0.0f;
-            } else if (L->absmax2 == nullptr) {
-                const float *am = reinterpret_cast<const float *>(L->absmax);
-                if (b0 + 16 <= L->nb && (i0 & 3) == 0) {
+                    for (int j = 0; j < 16; ++j) sc[j] = 0.0f;
+                } else if (L->absmax2 == nullptr) {
+                    const float *am = reinterpret_cast<const float *>(L->absmax);
+                    if (b0 + 16 <= L->nb && (i0 & 3) == 0) {
 #pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                        const float4 v = __ldg(reinterpret_cast<const float4 *>(am + i0) + q);
-                        sc[4 * q] = v.x; sc[4 * q + 1] = v.y; sc[4 * q + 2] = v.z; sc[4 * q + 3] = v.w;
+                        for (int q = 0; q < 4; ++q) {
+                            const float4 v = __ldg(reinterpret_cast<const float4 *>(am + i0) + q);
+                            sc[4 * q] = v.x; sc[4 * q + 1] = v.y; sc[4 * q + 2] = v.z; sc[4 * q + 3] = v.w;
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) sc[j] = (b0 + j < L->nb) ? __ldg(am + i0 + j) : 0.0f;
                     }
                 } else {
+                    // int8 code * (second-level maximum / 127); 16 consecutive blocks see at most two maxima
+                    const int8_t *aq = reinterpret_cast<const int8_t *>(L->absmax);
+                    const int last = (b0 + 15 < L->nb ? b0 + 15 : L->nb - 1) - b0;
+                    const float f0 = __ldg(L->absmax2 + (i0 >> 8)) * (1.0f / 127.0f);
+                    const float f1 = __ldg(L->absmax2 + ((i0 + last) >> 8)) * (1.0f / 127.0f);
+                    const int split = (int)(((i0 >> 8) + 1) * 256 - i0);          // first j that uses f1
+                    uint32_t raw[4];
+                    if (b0 + 16 <= L->nb && (i0 & 3) == 0) {
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) sc[j] = (b0 + j < L->nb) ? __ldg(am + i0 + j) : 0.0f;
-                }
-            } else {
-                // int8 code * (second-level maximum / 127); 16 consecutive blocks see at most two maxima
-                const int8_t *aq = reinterpret_cast<const int8_t *>(L->absmax);
-                const int last = (b0 + 15 < L->nb ? b0 + 15 : L->nb - 1) - b0;
-                const float f0 = __ldg(L->absmax2 + (i0 >> 8)) * (1.0f / 127.0f);
-                const float f1 = __ldg(L->absmax2 + ((i0 + last) >> 8)) * (1.0f / 127.0f);
-                const int split = (int)(((i0 >> 8) + 1) * 256 - i0);          // first j that uses f1
-                uint32_t raw[4];
-                if (b0 + 16 <= L->nb && (i0 & 3) == 0) {
+                        for (int q = 0; q < 4; ++q) raw[q] = __ldg(reinterpret_cast<const uint32_t *>(aq + i0) + q);
+                    } else {
 #pragma unroll
-                    for (int q = 0; q < 4; ++q) raw[q] = __ldg(reinterpret_cast<const uint32_t *>(aq + i0) + q);
-                } else {
+                        for (int q = 0; q < 4; ++q) {
+                            raw[q] = 0u;
 #pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                        raw[q] = 0u;
+                            for (int e = 0; e < 4; ++e)
+                                if (b0 + 4 * q + e < L->nb) raw[q] |= (uint32_t)(uint8_t)__ldg(aq + i0 + 4 * q + e) << (8 * e);
+                        }
+                    }
 #pragma unroll
-                        for (int e = 0; e < 4; ++e)
-                            if (b0 + 4 * q + e < L->nb) raw[q] |= (uint32_t)(uint8_t)__ldg(aq + i0 + 4 * q + e) << (8 * e);
+                    for (int j = 0; j < 16; ++j) {
+                        const int code = (int)(int8_t)((raw[j >> 2] >> (8 * (j & 3))) & 0xFFu);
+                        sc[j] = (b0 + j < L->nb) ? (float)code * (j < split ? f0 : f1) : 0.0f;
                     }
                 }
-#pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    const int code = (int)(int8_t)((raw[j >> 2] >> (8 * (j & 3))) & 0xFFu);
-                    sc[j] = (b0 + j < L->nb) ? (float)code * (j < split ? f0 : f1) : 0.0f;
+            };
+            int u = blockIdx.x;
+            StreamUnit un = {0, 0, 0, 0};
+            const StreamLinear *L = nullptr;
+            int s = 0, turn = 0, xslot = 0;  // turn: global stage index modulo SG_LOADERS
+            uint32_t xph = 0;
+            bool have = false;
+            auto step = [&]() {                  // to the next stage of the global sequence
+                ++s;
+                if (++turn == SG_LOADERS) turn = 0;
+                if (++xslot == nxs) { xslot = 0; xph ^= 1u; }
+            };
+            auto advance_to_mine = [&]() {       // positions the cursor on my next stage; returns false at the end
+                for (;;) {
+                    if (!have) {
+                        if (u >= a.nunits) return false;
+                        un = unit_of(u); L = lin_of(un.lin); s = un.s_begin; have = true;
+                    }
+                    if (s >= un.s_end) { have = false; u += gridDim.x; continue; }
+                    if (turn == me) return true;
+                    step();
                 }
-            }
-        };
-        // walk the global stage sequence; (u, s) of my next stage is found by stepping the cursor
-        int u = blockIdx.x;
-        StreamUnit un = {0, 0, 0, 0};
-        const StreamLinear *L = nullptr;
-        int s = 0, slot = 0, turn = 0;       // turn: global stage index modulo SG_LOADERS
-        uint32_t ph = 0;
-        bool have = false;
-        auto step = [&]() {                  // to the next stage of the global sequence
-            ++s;
-            if (++turn == SG_LOADERS) turn = 0;
-            if (++slot == nslots) { slot = 0; ph ^= 1u; }
-        };
-        auto advance_to_mine = [&]() {       // positions the cursor on my next stage; returns false at the end
-            for (;;) {
-                if (!have) {
-                    if (u >= a.nunits) return false;
-                    un = unit_of(u); L = lin_of(un.lin); s = un.s_begin; have = true;
-                }
-                if (s >= un.s_end) { have = false; u += gridDim.x; continue; }
-                if (turn == me) return true;
+            };
+            float cur[16];
+            bool more = advance_to_mine();
+            if (more) read_scales(L, un.row0, s, cur);
+            while (more && !*abort_flag) {
+                const int my_x = xslot, my_s = s;
+                const uint32_t my_ph = xph;
+                const StreamLinear *my_L = L;
                 step();
-            }
-        };
-        float cur[16];
-        bool more = advance_to_mine();
-        if (more) read_scales(L, un.row0, s, cur);
-        while (more && !*abort_flag) {
-            const int my_slot = slot, my_s = s;
-            const uint32_t my_ph = ph;
-            const StreamLinear *my_L = L;
-            step();
-            float nxt[16];
-            more = advance_to_mine();
-            if (more) read_scales(L, un.row0, s, nxt);
-            if (!mbar_wait_relaxed(empty_bar(my_slot), my_ph ^ 1u, abort_flag)) { atomicExch(&g_stream_status, 202); *abort_flag = 1; break; }
-            const uint32_t sb = sm.addr(my_slot);
+                float nxt[16];
+                more = advance_to_mine();
+                if (more) read_scales(L, un.row0, s, nxt);
+                if (!mbar_wait(xempty_bar(my_x), my_ph ^ 1u, abort_flag)) { atomicExch(&g_stream_status, 202); *abort_flag = 1; break; }
+                const uint32_t xb = s_xs + (uint32_t)my_x * xs_bytes;
 #pragma unroll
-            for (int j = 0; j < 16; ++j) sts_f32(sb + SG_W_BYTES + (j * 32 + lane) * 4, cur[j]);
-            if (!my_L->x_bulk_ok) {
-                // x: 1024 columns of every batch row, zero beyond K
-                const XT *x = reinterpret_cast<const XT *>(my_L->x);
-                const int k_base = my_s * (SG_STAGE_BLOCKS * 64);
-                for (int m = 0; m < a.M; ++m) {
-                    const XT *xr = x + (int64_t)m * my_L->x_ld;
-#pragma unroll
-                    for (int c4 = 0; c4 < 4; ++c4) {
-                        const int k0 = k_base + (lane + 32 * c4) * 8;
-                        uint16_t e[8];
-#pragma unroll
-                        for (int j = 0; j < 8; ++j)
-                            e[j] = (k0 + j < my_L->K) ? *reinterpret_cast<const uint16_t *>(xr + (k0 + j) % my_L->x_period) : (uint16_t)0;
-                        sts128(sb + SG_W_BYTES + SG_A_BYTES + m * SG_XPITCH + (lane + 32 * c4) * 16,
-                               make_uint4(e[0] | ((uint32_t)e[1] << 16), e[2] | ((uint32_t)e[3] << 16),
-                                          e[4] | ((uint32_t)e[5] << 16), e[6] | ((uint32_t)e[7] << 16)));
+                for (int j = 0; j < 16; ++j) sts_f32(xb + (j * 32 + lane) * 4, cur[j]);
+                int xcols = my_L->K - my_s * (SG_STAGE_BLOCKS * 64);
+                xcols = xcols > SG_STAGE_BLOCKS * 64 ? SG_STAGE_BLOCKS * 64 : (xcols < 0 ? 0 : xcols);
+                if (my_L->x_bulk_ok) {
+                    // x: one bulk copy per batch row, tracked by the slot's barrier (columns beyond K keep their zeros)
+                    __syncwarp();
+                    if (lane == 0) {
+                        const uint32_t nb2 = (uint32_t)xcols * 2u;
+                        mbar_arrive_expect_tx(xfull_bar(my_x), nb2 * (uint32_t)a.M);
+                        const int col = (my_s * (SG_STAGE_BLOCKS * 64)) % my_L->x_period;
+                        const unsigned char *src = reinterpret_cast<const unsigned char *>(my_L->x) + (int64_t)col * 2;
+#ifdef MPSBNB_SELFCHECK
+                        {
+                            const uint32_t d0 = xb + SG_A_BYTES, d1 = xb + SG_A_BYTES + (a.M - 1) * SG_XPITCH + nb2;
+                            if ((nb2 & 15u) || (d0 & 15u) || (reinterpret_cast<uintptr_t>(src) & 15) || ((my_L->x_ld * 2) & 15) ||
+                                d1 > xb + xs_bytes || xb + xs_bytes > sm.low0 || xcols < 0) {
+                                atomicExch(&g_stream_status, 301); *abort_flag = 1;
+                            }
+                        }
+                        if (*abort_flag) break;
+#endif
+                        if (nb2 != 0u)
+                            for (int m = 0; m < a.M; ++m)
+                                bulk_load_1d(xb + SG_A_BYTES + m * SG_XPITCH, src + (int64_t)m * my_L->x_ld * 2, nb2, xfull_bar(my_x));
                     }
-                }
-            }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(full_bar(my_slot));
+                } else {
+                    // x: 1024 columns of every batch row by plain loads, zero beyond K
+                    const XT *x = reinterpret_cast<const XT *>(my_L->x);
+                    const int k_base = my_s * (SG_STAGE_BLOCKS * 64);
+                    for (int m = 0; m < a.M; ++m) {
+                        const XT *xr = x + (int64_t)m * my_L->x_ld;
 #pragma unroll
-            for (int j = 0; j < 16; ++j) cur[j] = nxt[j];
+                        for (int c4 = 0; c4 < 4; ++c4) {
+                            const int k0 = k_base + (lane + 32 * c4) * 8;
+                            uint16_t e[8];
+#pragma unroll
+                            for (int j = 0; j < 8; ++j)
+                                e[j] = (k0 + j < my_L->K) ? *reinterpret_cast<const uint16_t *>(xr + (k0 + j) % my_L->x_period) : (uint16_t)0;
+                            sts128(xb + SG_A_BYTES + m * SG_XPITCH + (lane + 32 * c4) * 16,
+                                   make_uint4(e[0] | ((uint32_t)e[1] << 16), e[2] | ((uint32_t)e[3] << 16),
+                                              e[4] | ((uint32_t)e[5] << 16), e[6] | ((uint32_t)e[7] << 16)));
+                        }
+                    }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(xfull_bar(my_x));
+                }
+#pragma unroll
+                for (int j = 0; j < 16; ++j) cur[j] = nxt[j];
+            }
         }
     } else {
         // ------------------------------------------------------------ consumers
+        // Software pipeline, one stage deep: while the table loads and MMAs of stage s run from registers,
+        // the packed bytes of stage s + 1 are already on their way from the weight ring into the other
+        // register set, and that weight slot is handed back before the MMAs of stage s start.
         const int g = lane >> 2, t = lane & 3;
         const int rt = warp & 1, kg = warp >> 1;
         const int rho = ((2 * g) & 7) + (g >> 2);                // tile row of MMA row g (conflict-free permutation)
@@ -504,48 +546,105 @@ __global__ void __launch_bounds__(SG_THREADS, 1) gemv4_stream_kernel(const __gri
             const int box = blk >> 2, c = 2 * (blk & 3) + (t >> 1);
             const int r0 = 16 * rt + rho;
             woff[j] = (uint32_t)(box * 4096 + r0 * 128 + ((c ^ rho) << 4) + 8 * (t & 1));
-            xoff[j] = (uint32_t)(SG_W_BYTES + SG_A_BYTES + g * SG_XPITCH + (blk * 64 + 16 * t) * 2);
-            aoff[j] = (uint32_t)(SG_W_BYTES + (blk * 32 + r0) * 4);
+            xoff[j] = (uint32_t)(SG_A_BYTES + g * SG_XPITCH + (blk * 64 + 16 * t) * 2);
+            aoff[j] = (uint32_t)((blk * 32 + r0) * 4);
         }
-        const uint32_t hasx = g < a.M ? 1u : 0u;
-        uint32_t xr0[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u}, xr1[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
-        int slot = 0, uc = 0;
-        uint32_t ph = 0, sb = sm.addr(0);
-        for (int u = blockIdx.x; u < a.nunits && !*abort_flag; u += gridDim.x, ++uc) {
-            const StreamUnit un = unit_of(u);
-            const int nbv = lin_of(un.lin)->nbv;
-            float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-            bool ok = true;
-            for (int s = un.s_begin; s < un.s_end; ++s) {
-                if (!mbar_wait(full_bar(slot), ph, abort_flag)) { atomicExch(&g_stream_status, 203); *abort_flag = 1; ok = false; break; }
-                const int nvalid = nbv - (s * SG_STAGE_BLOCKS + 2 * kg);   // my blocks that hold real k (warp-uniform)
-                uint32_t w0[4], w1[4];
-                float am0[2], am1[2];
-                fetch_block(w0, am0, xr0, sb, woff[0], aoff[0], xoff[0], hasx);
-                fetch_block(w1, am1, xr1, sb, woff[1], aoff[1], xoff[1], hasx);
-                // the slot goes back to the producers as soon as its bytes are in registers: the arrive is
-                // queued behind the loads and, through `dep`, cannot issue before the last of them returned
-                const uint32_t dep = (w1[3] | __float_as_uint(am1[1])) & a.zero;
-                __syncwarp();
-                if (lane == 0) mbar_arrive(empty_bar(slot) + dep);
-                if (!(a.debug & 1)) {
-                    if (nvalid > 0) compute_block<XT>(acc, w0, am0, xr0, lane_word);
-                    if (nvalid > 1) compute_block<XT>(acc, w1, am1, xr1, lane_word);
-                }
-                if (++slot == nslots) { slot = 0; ph ^= 1u; }
-                sb = sm.addr(slot);
+        const bool hasx = g < a.M;
+        struct Cur { int u, s, s_end, nbv; bool valid; };
+        auto load_unit = [&](Cur &c) {
+            c.valid = c.u < a.nunits;
+            if (c.valid) { const StreamUnit un = unit_of(c.u); c.s = un.s_begin; c.s_end = un.s_end; c.nbv = lin_of(un.lin)->nbv; }
+        };
+        auto next_stage = [&](Cur &c) { if (++c.s == c.s_end) { c.u += gridDim.x; load_unit(c); } };
+        int slot = 0, xslot = 0, uc = 0;
+        uint32_t ph = 0, xph = 0;
+        float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        bool ok = true;
+        // waits for the next stage in the weight ring, pulls this warp's bytes into w, frees the slot
+#ifdef MPSBNB_PROF
+        long long p_fetch = 0, p_xwait = 0, p_comp = 0, p_end = 0;
+#endif
+        auto fetch = [&](uint32_t (&w)[8]) {
+            if (!mbar_wait(full_bar(slot), ph, abort_flag)) { atomicExch(&g_stream_status, 203); *abort_flag = 1; ok = false; return; }
+            const uint32_t sb = sm.addr(slot);
+#ifdef MPSBNB_SELFCHECK
+            if (slot >= nslots || (sb & 1023u) || woff[1] + 1024 + 8 > SG_W_BYTES || ((sb + woff[0]) & 7u) ||
+                sb + SG_W_BYTES > s_base + SG_SMEM_BYTES || (sb < SG_LUT_ABS && sb + SG_W_BYTES > SG_LUT_ABS)) {
+                atomicExch(&g_stream_status, 303); *abort_flag = 1; ok = false; return;
             }
-            if (!ok) break;
-            // hand the partial sums to the reducer warp; the buffer of two units ago must have been drained
-            const int buf = uc & 1;
-            if (!mbar_wait(red_empty(buf), ((uint32_t)(uc >> 1) & 1u) ^ 1u, abort_flag)) { atomicExch(&g_stream_status, 205); *abort_flag = 1; break; }
-            const uint32_t rb = s_red + (uint32_t)(buf * SG_RED_BYTES);
-#pragma unroll
-            for (int c = 0; c < 4; ++c)
-                sts_f32(rb + (uint32_t)(((warp * 8 + 2 * t + (c & 1)) * 20 + g + 8 * (c >> 1)) * 4), acc[c]);
+#endif
+            fetch_stage(w, sb + woff[0], sb + woff[1]);
+            // the arrive is queued behind the loads and, through `dep`, cannot issue before the last returned
+            const uint32_t dep = w[7] & a.zero;
             __syncwarp();
-            if (lane == 0) mbar_arrive(red_full(buf));
+            if (lane == 0) mbar_arrive(empty_bar(slot) + dep);
+            if (++slot == nslots) { slot = 0; ph ^= 1u; }
+        };
+        Cur cur; cur.u = (int)blockIdx.x; load_unit(cur);
+        uint32_t wA[8], wB[8];
+        if (cur.valid) fetch(wA);
+        // one iteration: start the fetch of the following stage into wn, then compute the current one from wc
+        auto iterate = [&](uint32_t (&wc)[8], uint32_t (&wn)[8]) {
+            const int nvalid = cur.nbv - (cur.s * SG_STAGE_BLOCKS + 2 * kg);   // my blocks that hold real k (warp-uniform)
+            const bool last = cur.s + 1 == cur.s_end;
+            PROF_T(q0);
+            next_stage(cur);
+            if (cur.valid) fetch(wn);
+            if (!ok) return;
+            PROF_T(q1);
+            if (!mbar_wait(xfull_bar(xslot), xph, abort_flag)) { atomicExch(&g_stream_status, 206); *abort_flag = 1; ok = false; return; }
+            const uint32_t xb = s_xs + (uint32_t)xslot * xs_bytes;
+            const uint32_t xa0 = hasx ? xb + xoff[0] : s_zero, xa1 = hasx ? xb + xoff[1] : s_zero;
+            PROF_T(q2);
+#ifdef MPSBNB_SELFCHECK
+            if ((xa0 & 15u) || (xa1 & 15u) || xa0 + 32 > sm.low0 || xa1 + 32 > sm.low0 || xb + aoff[1] + 36 > xb + SG_A_BYTES ||
+                xslot >= nxs) { atomicExch(&g_stream_status, 302); *abort_flag = 1; ok = false; return; }
+#endif
+            if (nvalid >= 2) StageOps<XT>::stage(acc, wc, xb + aoff[0], xb + aoff[1], xa0, xa1, lane_word);
+            else if (nvalid == 1) StageOps<XT>::block(acc, wc, xb + aoff[0], xa0, lane_word);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(xempty_bar(xslot) + (__float_as_uint(acc[0]) & a.zero));
+            if (++xslot == nxs) { xslot = 0; xph ^= 1u; }
+#ifdef MPSBNB_PROF
+            const long long q3 = clock64() + (long long)(__float_as_uint(acc[0]) & a.zero);
+            p_fetch += q1 - q0; p_xwait += q2 - q1; p_comp += q3 - q2;
+#endif
+            if (last) {
+                // hand the partial sums to the reducer warp; the buffer of two units ago must have been drained
+                const int buf = uc & 1;
+                if (!mbar_wait(red_empty(buf), ((uint32_t)(uc >> 1) & 1u) ^ 1u, abort_flag)) { atomicExch(&g_stream_status, 205); *abort_flag = 1; ok = false; return; }
+                const uint32_t rb = s_red + (uint32_t)(buf * SG_RED_BYTES);
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    sts_f32(rb + (uint32_t)(((warp * 8 + 2 * t + (c & 1)) * 20 + g + 8 * (c >> 1)) * 4), acc[c]);
+                    acc[c] = 0.0f;
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(red_full(buf));
+                ++uc;
+#ifdef MPSBNB_PROF
+                p_end += clock64() - q3;
+#endif
+            }
+        };
+        // `cur` runs one stage ahead inside iterate(); track whether a stage is pending with a flag
+        bool pending = cur.valid;
+        while (pending && ok && !*abort_flag) {
+            iterate(wA, wB);
+            pending = cur.valid;
+            if (!(pending && ok)) break;
+            iterate(wB, wA);
+            pending = cur.valid;
         }
+#ifdef MPSBNB_PROF
+        if (lane == 0) { long long *pp = g_prof + (blockIdx.x * 16 + warp) * 4; pp[0] = p_fetch; pp[1] = p_xwait; pp[2] = p_comp; pp[3] = p_end; }
+#endif
+    }
+    // After a time-out the roles leave early while copies may still be on their way into this CTA's
+    // shared memory: give them a bounded moment to land before the CTA retires.
+    if (*abort_flag) {
+        const long long t0 = clock64();
+        while (clock64() - t0 < 400000ll) { }
     }
 }
 
@@ -580,14 +679,32 @@ static int fill_linear(StreamLinear &L, const HostLinear &h, int y_dtype) {
     EncodeTiledFn fn = encode_tiled();
     if (fn == nullptr) return MPSBNB_ERR_NO_DEVICE;
     const int64_t Kp = padded_k(h.K, 64);
-    const cuuint64_t dims[2] = {(cuuint64_t)(Kp / 2), (cuuint64_t)h.N};
-    const cuuint64_t strides[1] = {(cuuint64_t)(Kp / 2)};
-    const cuuint32_t box[2] = {128u, (cuuint32_t)SG_ROWS};
-    const cuuint32_t estr[2] = {1u, 1u};
-    if (fn(&L.map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t *>(h.packed), dims, strides, box, estr,
-           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-        return MPSBNB_ERR_INVALID_ARG;
+    const int64_t row_bytes = Kp / 2;
+    CUresult cr = CUDA_ERROR_INVALID_VALUE;
+    L.map3d = 0;
+    if (row_bytes % 128 == 0) {
+        // 3-D view {128 B, N rows, row_bytes / 128 parts}: a box {128, 32, 4} lands as [part][row][128 B],
+        // the same shared-memory image as four 2-D boxes, with one instruction
+        const cuuint64_t dims[3] = {128u, (cuuint64_t)h.N, (cuuint64_t)(row_bytes / 128)};
+        const cuuint64_t strides[2] = {(cuuint64_t)row_bytes, 128u};
+        const cuuint32_t box[3] = {128u, (cuuint32_t)SG_ROWS, 4u};
+        const cuuint32_t estr[3] = {1u, 1u, 1u};
+        cr = fn(&L.map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<uint8_t *>(h.packed), dims, strides, box, estr,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        L.map3d = cr == CUDA_SUCCESS ? 1 : 0;
+    }
+    if (!L.map3d) {
+        const cuuint64_t dims[2] = {(cuuint64_t)row_bytes, (cuuint64_t)h.N};
+        const cuuint64_t strides[1] = {(cuuint64_t)row_bytes};
+        const cuuint32_t box[2] = {128u, (cuuint32_t)SG_ROWS};
+        const cuuint32_t estr[2] = {1u, 1u};
+        cr = fn(&L.map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t *>(h.packed), dims, strides, box, estr,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    }
+    if (cr != CUDA_SUCCESS) return MPSBNB_ERR_INVALID_ARG;
+    L.pad_ = 0;
     L.x = h.x; L.absmax = h.absmax; L.absmax2 = h.absmax2; L.bias = h.bias; L.y = h.y; L.acc = h.acc;
     L.x_ld = h.x_ld;
     L.N = (int)h.N; L.K = (int)h.K; L.nb = (int)(Kp / 64); L.nbv = (int)((h.K + 63) / 64);
@@ -598,23 +715,9 @@ static int fill_linear(StreamLinear &L, const HostLinear &h, int y_dtype) {
     return MPSBNB_OK;
 }
 
-static int slot_bytes_for(int M) { return SG_W_BYTES + SG_A_BYTES + ((M * SG_XPITCH + 1023) / 1024) * 1024; }
-
-// lower bound of the slot count the kernel will find (it derives the exact map from its shared base)
-static int slots_for(int M) {
-    const int low = (128 * 1024 - 2 * SG_RED_BYTES - 256 - 2048) / slot_bytes_for(M);
-    const int high = (227 * 1024 - 192 * 1024) / slot_bytes_for(M);
-    const int n = low + high;
-    return n > SG_MAX_SLOTS ? SG_MAX_SLOTS : n;
-}
-
 template <typename XT>
-static int launch_stream(StreamArgs &args, cudaStream_t st) {
-    args.slot_bytes = slot_bytes_for(args.M);
-    { const char *e = getenv("MPSBNB_STREAM_DEBUG"); args.debug = e ? atoi(e) : 0; }   // DEBUGVAR
+static int launch_stream(StreamArgs &args, cudaStream_t st, bool pdl = false) {
     args.zero = 0u;
-    args.nslots = slots_for(args.M);
-    if (args.nslots < 2) return MPSBNB_ERR_UNSUPPORTED;
     const int smem = SG_SMEM_BYTES;
     static int configured[64] = {};
     int dev = 0;
@@ -625,10 +728,22 @@ static int launch_stream(StreamArgs &args, cudaStream_t st) {
     }
     int grid = sm_count();
     if (grid > args.nunits) grid = args.nunits;
-    gemv4_stream_kernel<XT><<<grid, SG_THREADS, smem, st>>>(args);
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3((unsigned)grid); cfg.blockDim = dim3(SG_THREADS); cfg.dynamicSmemBytes = (size_t)smem; cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = pdl ? 1 : 0;
+    MPSBNB_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemv4_stream_kernel<XT>, args));
     return check_launch();
 }
 
+#ifdef MPSBNB_PROF
+}  // namespace mpsbnb
+extern "C" int mpsbnb_debug_prof(long long *out) { return cudaMemcpyFromSymbol(out, mpsbnb::g_prof, sizeof(long long) * 148 * 16 * 4) == cudaSuccess ? 0 : -3; }
+namespace mpsbnb {
+#endif
 int stream_status_fetch(int *out, bool reset) {
     MPSBNB_CUDA_TRY(cudaMemcpyFromSymbol(out, g_stream_status, sizeof(int)));
     if (reset) {
@@ -734,7 +849,7 @@ extern "C" int mpsbnb_gemv_4bit_group_plan(const mpsbnb_linear4_desc *descs, int
     plan_out->M = (int)M;
     plan_out->x_dtype = x_dtype;
     plan_out->quant_type = quant_type;
-    plan_out->reserved = 0;
+    plan_out->flags = 0;
     return MPSBNB_OK;
 }
 
@@ -745,6 +860,7 @@ extern "C" int mpsbnb_gemv_4bit_group_run(const mpsbnb_group_plan *plan, void *s
     args.lins = reinterpret_cast<const StreamLinear *>(plan->dev);
     args.units = reinterpret_cast<const StreamUnit *>(reinterpret_cast<const unsigned char *>(plan->dev) + plan->units_offset);
     args.nunits = plan->n_units; args.M = plan->M; args.quant_type = plan->quant_type;
-    return plan->x_dtype == MPSBNB_F16 ? launch_stream<__half>(args, (cudaStream_t)stream)
-                                       : launch_stream<__nv_bfloat16>(args, (cudaStream_t)stream);
+    const bool pdl = (plan->flags & MPSBNB_GROUP_PDL) != 0;
+    return plan->x_dtype == MPSBNB_F16 ? launch_stream<__half>(args, (cudaStream_t)stream, pdl)
+                                       : launch_stream<__nv_bfloat16>(args, (cudaStream_t)stream, pdl);
 }

@@ -95,10 +95,12 @@ class LayerStack:
 
     def __init__(self, cfg: StackConfig, device, quant_type: str = "nf4", double_quant: bool = True,
                  layers: Optional[int] = None, rank: int = 0, world: int = 1, seed: int = 1000,
-                 dtype: torch.dtype = torch.float16, group=None):
+                 dtype: torch.dtype = torch.float16, group=None, use_pdl: bool = True):
         self.cfg, self.device, self.dtype = cfg, torch.device(device), dtype
         self.layers = cfg.layers if layers is None else layers
         self.rank, self.world, self.group = rank, world, group
+        # programmatic dependent launch between the per-layer kernels (single GPU: no NCCL kernel in between)
+        self.use_pdl = use_pdl and world == 1
         self.quant_type, self.double_quant = quant_type, double_quant
         self.alpha = cfg.alpha()
         if cfg.hidden % world or cfg.ffn % world or cfg.kv % world:
@@ -168,6 +170,7 @@ class LayerStack:
             N.check(lib.mpsbnb_gemv_4bit_group_plan(descs, C.c_int(7), N.i64(M), N.dt(self.dtype), N.dt(self.dtype),
                                                     C.c_int(N.qt(self.quant_type)), N.ptr(mem), C.c_size_t(nbytes),
                                                     C.byref(plan), N.stream()), "gemv_4bit_group_plan")
+            plan.flags = N.GROUP_PDL if self.use_pdl else 0
             self._plans.append(plan)
             self._plan_mem.append(mem)
 
@@ -193,7 +196,8 @@ class LayerStack:
                 N.check(lib.mpsbnb_gemv_4bit_group_run(C.byref(self._plans[l]), N.stream()), "gemv_4bit_group_run")
                 dst = self.h if g == 1 else self.h_shard
                 N.check(lib.mpsbnb_stack_boundary_acc(N.ptr(self.acc), C.c_float(self.alpha), N.i64(M * hs), N.ptr(dst),
-                                                      N.dt(self.dtype), N.stream()), "stack_boundary_acc")
+                                                      N.dt(self.dtype), C.c_int(N.GROUP_PDL if self.use_pdl else 0),
+                                                      N.stream()), "stack_boundary_acc")
                 if g > 1:
                     torch.distributed.all_gather_into_tensor(self.gathered.view(g * M, -1), self.h_shard, group=self.group)
                     N.check(lib.mpsbnb_stack_expand(N.ptr(self.gathered), N.dt(self.dtype), N.i64(g), N.i64(M),
