@@ -1,6 +1,7 @@
 """Benchmark of the fused dequantise-matmul hot path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--batch M]
+                    [--layers L] [--skip-extras]
 
 Workload (N = 1): the Llama-2-7B-shaped NF4 decode stack of BASELINE config 3 — 32 layers x
 {q,k,v,o 4096x4096, gate/up 11008x4096, down 4096x11008}, double-quantised absmax, fp16,
@@ -13,6 +14,11 @@ Prints ONE JSON line: metric nf4_decode_gbs = algorithmic bytes per step / step 
 the HBM roofline, an end-to-end figure through the public LayerStack API with host buffers,
 a CPU baseline (the C oracle of the reference's CPU path on this host's cores), and, at
 N = 1, the prefill GEMM of BASELINE config 2 (FP4, 2048 x 4096 x 11008) as a second object.
+
+--layers L runs a stack of only L layers (a reduced workload for profiler captures; the JSON
+line names it) and --skip-extras leaves out the prefill object and the CPU baseline.  The timed
+region is bracketed by cudaProfilerStart/Stop so that a profiler started with
+--profile-from-start off sees exactly the timed launches.
 
 --impl reference times the reference's CPU algorithm (the C oracle: dequantise the whole
 weight, then matmul, as mps_bitsandbytes/functional.py:752-773 does on CPU) on one layer of
@@ -191,7 +197,7 @@ def run_gpu(args, cfg):
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     peaks = load_peaks()
     M = args.batch
-    stack = S.LayerStack(cfg, device=f"cuda:{local}", rank=rank, world=world)
+    stack = S.LayerStack(cfg, device=f"cuda:{local}", rank=rank, world=world, layers=args.layers)
     stack.prepare(M, use_graph=True)
     gen = torch.Generator(device="cpu"); gen.manual_seed(1)
     x_host = torch.randn(M, cfg.hidden, generator=gen).half().pin_memory()
@@ -212,11 +218,13 @@ def run_gpu(args, cfg):
         sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
+    torch.cuda.profiler.start()
     e0.record()
     for _ in range(args.steps):
         stack.step()
     e1.record()
     barrier()
+    torch.cuda.profiler.stop()
     ms = e0.elapsed_time(e1) / args.steps
     # ---- end to end: pinned host input -> device, all layers, result back to host, every step
     for _ in range(3):
@@ -236,7 +244,7 @@ def run_gpu(args, cfg):
         ms, e2e_ms = float(t[0]), float(t[1])
     finite = bool(torch.isfinite(stack.h.float()).all())
 
-    nbytes = S.algorithmic_bytes(cfg, M)                         # whole model, all ranks together
+    nbytes = S.algorithmic_bytes(cfg, M, layers=stack.layers)    # whole model, all ranks together
     gbs = nbytes / (ms * 1e-3) / 1e9
     e2e_gbs = nbytes / (e2e_ms * 1e-3) / 1e9
     out = None
@@ -251,7 +259,7 @@ def run_gpu(args, cfg):
             "vs_baseline": None, "dtype": "f16", "data": "synthetic",
             "config": {"workload": f"{cfg.name} NF4+DQ decode stack ({stack.layers} layers x 7 Linear4bit), batch {M}, "
                                    f"N-sharded over {world} GPU(s)", "batch": M, "layers": stack.layers,
-                       "l2": "inputs (3.3 GB of weights per step) larger than L2; no flush needed",
+                       "l2": f"inputs ({nbytes / 1e9:.2f} GB of weights per step) larger than L2; no flush needed",
                        "parallelism": f"n-shard{world}", "outputs_finite": finite},
             "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                          "frac": per_gpu / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"],
@@ -267,7 +275,7 @@ def run_gpu(args, cfg):
     if world > 1:
         dist.barrier()
     if rank == 0:
-        if world == 1:
+        if world == 1 and not args.skip_extras:
             del stack
             torch.cuda.empty_cache()
             try:
@@ -288,6 +296,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--model", default="llama2-7b", choices=["llama2-7b", "llama-70b"])
+    ap.add_argument("--layers", type=int, default=None, help="reduced depth, for profiler captures")
+    ap.add_argument("--skip-extras", action="store_true", help="no prefill object, no CPU baseline")
     args = ap.parse_args()
     from mps_bitsandbytes_b200 import stack as S
     cfg = S.LLAMA2_7B if args.model == "llama2-7b" else S.LLAMA_70B
