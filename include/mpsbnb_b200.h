@@ -174,6 +174,26 @@ int mpsbnb_gemm_4bit(const void *x, int x_dtype, int64_t M, const uint8_t *packe
                      int blocksize, int quant_type, const void *bias, void *y, int y_dtype,
                      void *workspace, size_t workspace_bytes, void *stream);
 
+/* mpsbnb_gemm_4bit without a workspace argument and without any allocation: the expanded
+ * weight goes into a fixed 32 MiB array inside the library's device image, shared by all
+ * calls on a device.  No counterpart in the reference (whose wrappers allocate from the
+ * PyTorch allocator on every call); it exists for hosts that own all device memory
+ * themselves and cannot provide a workspace.
+ *  - Limit: mpsbnb_gemm_4bit_static_bytes(x, M, N, K) <= mpsbnb_gemm_4bit_static_max_bytes()
+ *    (N * roundup8(K) * 2 bytes, plus M * roundup8(K) * 2 when K % 8 != 0 or x is not
+ *    16-byte aligned); larger problems return MPSBNB_ERR_TOO_LARGE and enqueue nothing.
+ *  - The first call on each device resolves the array's address (set-up, not a stream
+ *    operation): make it before any stream capture that will hold later calls.
+ *  - Calls that may overlap in time on different streams of one device race on the array;
+ *    same-stream calls are ordered.  Nothing in the array needs to start at zero.
+ * Results are identical to mpsbnb_gemm_4bit (same kernels, same order). */
+size_t mpsbnb_gemm_4bit_static_max_bytes(void);
+size_t mpsbnb_gemm_4bit_static_bytes(const void *x, int64_t M, int64_t N, int64_t K);
+int mpsbnb_gemm_4bit_static(const void *x, int x_dtype, int64_t M, const uint8_t *packed,
+                            const void *absmax, const float *absmax2, int64_t N, int64_t K,
+                            int blocksize, int quant_type, const void *bias, void *y,
+                            int y_dtype, void *stream);
+
 /* Dense tensor-core GEMM y[M,N] = a[M,K] . b[N,K]^T (+ bias), both operands K-major in
  * ab_dtype (F16/BF16) with leading dimensions lda / ldb in elements (multiples of 8, bases
  * 16-byte aligned: TMA row pitches), fp32 accumulation in tensor memory.  Building block of
