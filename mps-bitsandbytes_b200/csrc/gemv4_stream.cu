@@ -28,6 +28,8 @@
 //            the HBM stream does not pause at unit boundaries.
 // All waits are bounded (see sm100.cuh); a time-out sets the device status word.
 #include "common.cuh"
+#include <cstdio>
+#include <cstdlib>
 #include "ops.cuh"
 #include "sm100.cuh"
 
@@ -39,6 +41,9 @@ namespace mpsbnb {
 using namespace sm100;
 
 constexpr int SG_CONSUMERS = 16;
+constexpr int SG_GROUPS = 4;                             // independent consumer groups (each takes every 4th stage)
+constexpr int SG_GROUP_WARPS = SG_CONSUMERS / SG_GROUPS;
+constexpr int SG_ITEMS = 8 / (SG_GROUP_WARPS / 2);       // block pairs a warp works through per stage
 constexpr int SG_LOADERS = 4;                           // must equal SG_MAX_XS (see there)
 constexpr int SG_THREADS = (SG_CONSUMERS + 1 + SG_LOADERS + 1) * 32;   // + TMA warp + reducer warp
 constexpr int SG_ROWS = 32;                              // weight rows per unit
@@ -86,6 +91,8 @@ struct StreamArgs {
     const StreamUnit *units;  // device array, or nullptr: unit u = rows [32 u, 32 u + 32) x all stages of `one`
     int nunits, M, quant_type;
     uint32_t zero;            // always 0; known only at run time (orders the slot release after the loads)
+    uint32_t sleep_cons;      // ns a consumer warp sleeps between probes of a barrier that is not ready
+    uint32_t sleep_other;     // same for the producer, loader and reducer warps
     StreamLinear one;
 };
 
@@ -162,10 +169,16 @@ __device__ __forceinline__ void fetch_stage(uint32_t (&w)[8], uint32_t wa0, uint
         ".reg .b32 ad, x<8>, y<8>;\n\t"                                                                     \
         ".reg .b32 f<16>, g<16>;\n\t"                                                                       \
         ".reg .f32 m<4>, t<4>, u<4>, z;\n\t"                                                                \
-        "ld.shared.v4.u32 {x0, x1, x2, x3}, [%14];\n\t"                                                     \
-        "ld.shared.v4.u32 {x4, x5, x6, x7}, [%14+16];\n\t"                                                  \
-        "ld.shared.v4.u32 {y0, y1, y2, y3}, [%15];\n\t"                                                     \
-        "ld.shared.v4.u32 {y4, y5, y6, y7}, [%15+16];\n\t"                                                  \
+        ".reg .pred px;\n\t"                                                                                \
+        "setp.ne.u32 px, %17, 0;\n\t"                                                                       \
+        "mov.b32 x0, 0;\n\t mov.b32 x1, 0;\n\t mov.b32 x2, 0;\n\t mov.b32 x3, 0;\n\t"                       \
+        "mov.b32 x4, 0;\n\t mov.b32 x5, 0;\n\t mov.b32 x6, 0;\n\t mov.b32 x7, 0;\n\t"                       \
+        "mov.b32 y0, 0;\n\t mov.b32 y1, 0;\n\t mov.b32 y2, 0;\n\t mov.b32 y3, 0;\n\t"                       \
+        "mov.b32 y4, 0;\n\t mov.b32 y5, 0;\n\t mov.b32 y6, 0;\n\t mov.b32 y7, 0;\n\t"                       \
+        "@px ld.shared.v4.u32 {x0, x1, x2, x3}, [%14];\n\t"                                                 \
+        "@px ld.shared.v4.u32 {x4, x5, x6, x7}, [%14+16];\n\t"                                              \
+        "@px ld.shared.v4.u32 {y0, y1, y2, y3}, [%15];\n\t"                                                 \
+        "@px ld.shared.v4.u32 {y4, y5, y6, y7}, [%15+16];\n\t"                                              \
         "ld.shared.f32 m0, [%12];\n\t"                                                                      \
         "ld.shared.f32 m1, [%12+32];\n\t"                                                                   \
         "ld.shared.f32 m2, [%13];\n\t"                                                                      \
@@ -188,7 +201,7 @@ __device__ __forceinline__ void fetch_stage(uint32_t (&w)[8], uint32_t wa0, uint
         "}\n"                                                                                               \
         : "+f"(acc[0]), "+f"(acc[1]), "+f"(acc[2]), "+f"(acc[3])                                            \
         : "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]),           \
-          "r"(aa0), "r"(aa1), "r"(xa0), "r"(xa1), "r"(lw)                                                   \
+          "r"(aa0), "r"(aa1), "r"(xa0), "r"(xa1), "r"(lw), "r"(hasx)                                        \
         : "memory")
 
 // compute_block: one block only (the ragged last stage of a row whose K is not a multiple of 128)
@@ -198,8 +211,12 @@ __device__ __forceinline__ void fetch_stage(uint32_t (&w)[8], uint32_t wa0, uint
         ".reg .b32 ad, x<8>;\n\t"                                                                           \
         ".reg .b32 f<16>;\n\t"                                                                              \
         ".reg .f32 m<2>, t<4>, z;\n\t"                                                                      \
-        "ld.shared.v4.u32 {x0, x1, x2, x3}, [%9];\n\t"                                                      \
-        "ld.shared.v4.u32 {x4, x5, x6, x7}, [%9+16];\n\t"                                                   \
+        ".reg .pred px;\n\t"                                                                                \
+        "setp.ne.u32 px, %11, 0;\n\t"                                                                       \
+        "mov.b32 x0, 0;\n\t mov.b32 x1, 0;\n\t mov.b32 x2, 0;\n\t mov.b32 x3, 0;\n\t"                       \
+        "mov.b32 x4, 0;\n\t mov.b32 x5, 0;\n\t mov.b32 x6, 0;\n\t mov.b32 x7, 0;\n\t"                       \
+        "@px ld.shared.v4.u32 {x0, x1, x2, x3}, [%9];\n\t"                                                  \
+        "@px ld.shared.v4.u32 {x4, x5, x6, x7}, [%9+16];\n\t"                                               \
         "ld.shared.f32 m0, [%8];\n\t"                                                                       \
         "ld.shared.f32 m1, [%8+32];\n\t"                                                                    \
         "mov.f32 z, 0f00000000;\n\t"                                                                        \
@@ -212,21 +229,21 @@ __device__ __forceinline__ void fetch_stage(uint32_t (&w)[8], uint32_t wa0, uint
         "fma.rn.f32 %2, m1, t2, %2;\n\t fma.rn.f32 %3, m1, t3, %3;\n\t"                                     \
         "}\n"                                                                                               \
         : "+f"(acc[0]), "+f"(acc[1]), "+f"(acc[2]), "+f"(acc[3])                                            \
-        : "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(aa0), "r"(xa0), "r"(lw)                           \
+        : "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(aa0), "r"(xa0), "r"(lw), "r"(hasx)                \
         : "memory")
 
 template <typename XT> struct StageOps;
 template <> struct StageOps<__half> {
     static __device__ __forceinline__ void stage(float (&acc)[4], const uint32_t (&w)[8], uint32_t aa0, uint32_t aa1,
-                                                 uint32_t xa0, uint32_t xa1, uint32_t lw) { MPSBNB_STAGE_ASM("f16"); }
+                                                 uint32_t xa0, uint32_t xa1, uint32_t lw, uint32_t hasx) { MPSBNB_STAGE_ASM("f16"); }
     static __device__ __forceinline__ void block(float (&acc)[4], const uint32_t (&w)[8], uint32_t aa0, uint32_t xa0,
-                                                 uint32_t lw) { MPSBNB_BLOCK_ASM("f16"); }
+                                                 uint32_t lw, uint32_t hasx) { MPSBNB_BLOCK_ASM("f16"); }
 };
 template <> struct StageOps<__nv_bfloat16> {
     static __device__ __forceinline__ void stage(float (&acc)[4], const uint32_t (&w)[8], uint32_t aa0, uint32_t aa1,
-                                                 uint32_t xa0, uint32_t xa1, uint32_t lw) { MPSBNB_STAGE_ASM("bf16"); }
+                                                 uint32_t xa0, uint32_t xa1, uint32_t lw, uint32_t hasx) { MPSBNB_STAGE_ASM("bf16"); }
     static __device__ __forceinline__ void block(float (&acc)[4], const uint32_t (&w)[8], uint32_t aa0, uint32_t xa0,
-                                                 uint32_t lw) { MPSBNB_BLOCK_ASM("bf16"); }
+                                                 uint32_t lw, uint32_t hasx) { MPSBNB_BLOCK_ASM("bf16"); }
 };
 
 // Shared-memory map, in ABSOLUTE shared-window addresses.  The code-pair table sits at exactly
@@ -273,6 +290,7 @@ __global__ void __launch_bounds__(SG_THREADS, 1) gemv4_stream_kernel(const __gri
         const int nhigh = (int)((s_base + (uint32_t)SG_SMEM_BYTES - SG_HIGH_ABS) / SG_W_BYTES);
         const int n = sm.nlow + nhigh;
         sm.nslots = n > SG_MAX_SLOTS ? SG_MAX_SLOTS : n;
+        sm.nslots -= sm.nslots % SG_GROUPS;                          // every slot belongs to one consumer group
         if (sm.nlow > sm.nslots) sm.nlow = sm.nslots;
     }
     const int nslots = sm.nslots;
@@ -289,9 +307,9 @@ __global__ void __launch_bounds__(SG_THREADS, 1) gemv4_stream_kernel(const __gri
     pdl_launch_dependents();
 
     if (tid == 0) {
-        for (int s = 0; s < nslots; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), SG_CONSUMERS); }
+        for (int s = 0; s < nslots; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), SG_GROUP_WARPS); }
         for (int b = 0; b < 2; ++b) { mbar_init(red_full(b), SG_CONSUMERS); mbar_init(red_empty(b), 1); }
-        for (int s = 0; s < nxs; ++s) { mbar_init(xfull_bar(s), 1); mbar_init(xempty_bar(s), SG_CONSUMERS); }
+        for (int s = 0; s < nxs; ++s) { mbar_init(xfull_bar(s), 1); mbar_init(xempty_bar(s), SG_GROUP_WARPS); }
         *abort_flag = 0;
         fence_mbar_init();
     }
@@ -339,7 +357,7 @@ __global__ void __launch_bounds__(SG_THREADS, 1) gemv4_stream_kernel(const __gri
                 const bool m3 = L->map3d != 0;
                 bool ok = true;
                 for (int s = un.s_begin; s < un.s_end; ++s) {
-                    if (!mbar_wait(empty_bar(slot), ph ^ 1u, abort_flag)) { atomicExch(&g_stream_status, 201); *abort_flag = 1; ok = false; break; }
+                    if (!mbar_wait_sleep(empty_bar(slot), ph ^ 1u, abort_flag, a.sleep_other)) { atomicExch(&g_stream_status, 201); *abort_flag = 1; ok = false; break; }
                     const uint32_t bar = full_bar(slot), dst = sm.addr(slot);
 #ifdef MPSBNB_SELFCHECK
                     if ((dst & 1023u) || dst + SG_W_BYTES > s_base + SG_SMEM_BYTES || (dst < SG_LUT_ABS && dst + SG_W_BYTES > SG_LUT_ABS) ||
@@ -372,7 +390,7 @@ __global__ void __launch_bounds__(SG_THREADS, 1) gemv4_stream_kernel(const __gri
             const StreamUnit un = unit_of(u);
             const StreamLinear *L = lin_of(un.lin);
             const int buf = uc & 1;
-            if (!mbar_wait(red_full(buf), (uint32_t)(uc >> 1) & 1u, abort_flag)) { atomicExch(&g_stream_status, 204); *abort_flag = 1; break; }
+            if (!mbar_wait_sleep(red_full(buf), (uint32_t)(uc >> 1) & 1u, abort_flag, a.sleep_other)) { atomicExch(&g_stream_status, 204); *abort_flag = 1; break; }
             const float *red = reinterpret_cast<const float *>(p_generic0 + s_red + buf * SG_RED_BYTES);
             const int n = un.row0 + lane;
             for (int m = 0; m < a.M; ++m) {
@@ -477,7 +495,7 @@ __global__ void __launch_bounds__(SG_THREADS, 1) gemv4_stream_kernel(const __gri
                 float nxt[16];
                 more = advance_to_mine();
                 if (more) read_scales(L, un.row0, s, nxt);
-                if (!mbar_wait(xempty_bar(my_x), my_ph ^ 1u, abort_flag)) { atomicExch(&g_stream_status, 202); *abort_flag = 1; break; }
+                if (!mbar_wait_sleep(xempty_bar(my_x), my_ph ^ 1u, abort_flag, a.sleep_other)) { atomicExch(&g_stream_status, 202); *abort_flag = 1; break; }
                 const uint32_t xb = s_xs + (uint32_t)my_x * xs_bytes;
 #pragma unroll
                 for (int j = 0; j < 16; ++j) sts_f32(xb + (j * 32 + lane) * 4, cur[j]);
@@ -532,87 +550,85 @@ __global__ void __launch_bounds__(SG_THREADS, 1) gemv4_stream_kernel(const __gri
         }
     } else {
         // ------------------------------------------------------------ consumers
-        // Software pipeline, one stage deep: while the table loads and MMAs of stage s run from registers,
-        // the packed bytes of stage s + 1 are already on their way from the weight ring into the other
-        // register set, and that weight slot is handed back before the MMAs of stage s start.
+        // The 16 warps form SG_GROUPS independent groups; group q takes every SG_GROUPS-th stage of the
+        // CTA's stage sequence, so the groups drift apart in time and one group's barrier waits are covered
+        // by the table loads and MMAs of the others.  Inside a group of W = 16 / SG_GROUPS warps, warp j owns
+        // row tile j & 1 and the block pairs kg = (j >> 1) + (W / 2) i, i = 0 .. SG_ITEMS - 1, of each stage:
+        // while item i runs from one register set, the packed bytes of item i + 1 are on their way into the
+        // other.  The weight slot is handed back when the last item's bytes are in registers, the scale/x
+        // slot after the last MMA.
         const int g = lane >> 2, t = lane & 3;
-        const int rt = warp & 1, kg = warp >> 1;
+        const int grp = warp / SG_GROUP_WARPS, j = warp % SG_GROUP_WARPS;
+        const int rt = j & 1, kg0 = j >> 1;
         const int rho = ((2 * g) & 7) + (g >> 2);                // tile row of MMA row g (conflict-free permutation)
         const uint32_t lane_word = SG_LUT_ABS | ((uint32_t)lane * 4u);   // bytes 0, 2, 3 of every table address
+        // offsets of item 0; item i adds SG_ITEM_W / SG_ITEM_X bytes
         uint32_t woff[2], xoff[2], aoff[2];
 #pragma unroll
-        for (int j = 0; j < 2; ++j) {
-            const int blk = 2 * kg + j;
+        for (int b = 0; b < 2; ++b) {
+            const int blk = 2 * kg0 + b;
             const int box = blk >> 2, c = 2 * (blk & 3) + (t >> 1);
             const int r0 = 16 * rt + rho;
-            woff[j] = (uint32_t)(box * 4096 + r0 * 128 + ((c ^ rho) << 4) + 8 * (t & 1));
-            xoff[j] = (uint32_t)(SG_A_BYTES + g * SG_XPITCH + (blk * 64 + 16 * t) * 2);
-            aoff[j] = (uint32_t)((blk * 32 + r0) * 4);
+            woff[b] = (uint32_t)(box * 4096 + r0 * 128 + ((c ^ rho) << 4) + 8 * (t & 1));
+            xoff[b] = (uint32_t)(SG_A_BYTES + g * SG_XPITCH + (blk * 64 + 16 * t) * 2);
+            aoff[b] = (uint32_t)((blk * 32 + r0) * 4);
         }
-        const bool hasx = g < a.M;
-        struct Cur { int u, s, s_end, nbv; bool valid; };
-        auto load_unit = [&](Cur &c) {
-            c.valid = c.u < a.nunits;
-            if (c.valid) { const StreamUnit un = unit_of(c.u); c.s = un.s_begin; c.s_end = un.s_end; c.nbv = lin_of(un.lin)->nbv; }
-        };
-        auto next_stage = [&](Cur &c) { if (++c.s == c.s_end) { c.u += gridDim.x; load_unit(c); } };
-        int slot = 0, xslot = 0, uc = 0;
-        uint32_t ph = 0, xph = 0;
+        constexpr int KG_STEP = SG_GROUP_WARPS / 2;                  // block pairs between two items of a warp
+        constexpr uint32_t ITEM_W = (uint32_t)(KG_STEP * 2 * 1024);   // 2 blocks = half a 4 KiB box
+        constexpr uint32_t ITEM_X = (uint32_t)(KG_STEP * 2 * 64 * 2); // x bytes per block pair step
+        constexpr uint32_t ITEM_A = (uint32_t)(KG_STEP * 2 * 32 * 4); // scale bytes per block pair step
+        const uint32_t hasx = g < a.M ? 1u : 0u;
+        int slot = grp % nslots, xslot = grp % nxs;              // ring positions of my next stage
+        uint32_t ph = (uint32_t)(grp / nslots) & 1u, xph = (uint32_t)(grp / nxs) & 1u;
+        int nextq = grp;                                          // my next stage in the CTA's stage sequence
+        int qb = 0, uc = 0;
         float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
         bool ok = true;
-        // waits for the next stage in the weight ring, pulls this warp's bytes into w, frees the slot
-#ifdef MPSBNB_PROF
-        long long p_fetch = 0, p_xwait = 0, p_comp = 0, p_end = 0;
-#endif
-        auto fetch = [&](uint32_t (&w)[8]) {
-            if (!mbar_wait(full_bar(slot), ph, abort_flag)) { atomicExch(&g_stream_status, 203); *abort_flag = 1; ok = false; return; }
-            const uint32_t sb = sm.addr(slot);
-#ifdef MPSBNB_SELFCHECK
-            if (slot >= nslots || (sb & 1023u) || woff[1] + 1024 + 8 > SG_W_BYTES || ((sb + woff[0]) & 7u) ||
-                sb + SG_W_BYTES > s_base + SG_SMEM_BYTES || (sb < SG_LUT_ABS && sb + SG_W_BYTES > SG_LUT_ABS)) {
-                atomicExch(&g_stream_status, 303); *abort_flag = 1; ok = false; return;
-            }
-#endif
-            fetch_stage(w, sb + woff[0], sb + woff[1]);
-            // the arrive is queued behind the loads and, through `dep`, cannot issue before the last returned
-            const uint32_t dep = w[7] & a.zero;
-            __syncwarp();
-            if (lane == 0) mbar_arrive(empty_bar(slot) + dep);
-            if (++slot == nslots) { slot = 0; ph ^= 1u; }
-        };
-        Cur cur; cur.u = (int)blockIdx.x; load_unit(cur);
         uint32_t wA[8], wB[8];
-        if (cur.valid) fetch(wA);
-        // one iteration: start the fetch of the following stage into wn, then compute the current one from wc
-        auto iterate = [&](uint32_t (&wc)[8], uint32_t (&wn)[8]) {
-            const int nvalid = cur.nbv - (cur.s * SG_STAGE_BLOCKS + 2 * kg);   // my blocks that hold real k (warp-uniform)
-            const bool last = cur.s + 1 == cur.s_end;
-            PROF_T(q0);
-            next_stage(cur);
-            if (cur.valid) fetch(wn);
-            if (!ok) return;
-            PROF_T(q1);
-            if (!mbar_wait(xfull_bar(xslot), xph, abort_flag)) { atomicExch(&g_stream_status, 206); *abort_flag = 1; ok = false; return; }
-            const uint32_t xb = s_xs + (uint32_t)xslot * xs_bytes;
-            const uint32_t xa0 = hasx ? xb + xoff[0] : s_zero, xa1 = hasx ? xb + xoff[1] : s_zero;
-            PROF_T(q2);
-#ifdef MPSBNB_SELFCHECK
-            if ((xa0 & 15u) || (xa1 & 15u) || xa0 + 32 > sm.low0 || xa1 + 32 > sm.low0 || xb + aoff[1] + 36 > xb + SG_A_BYTES ||
-                xslot >= nxs) { atomicExch(&g_stream_status, 302); *abort_flag = 1; ok = false; return; }
-#endif
-            if (nvalid >= 2) StageOps<XT>::stage(acc, wc, xb + aoff[0], xb + aoff[1], xa0, xa1, lane_word);
-            else if (nvalid == 1) StageOps<XT>::block(acc, wc, xb + aoff[0], xa0, lane_word);
-            __syncwarp();
-            if (lane == 0) mbar_arrive(xempty_bar(xslot) + (__float_as_uint(acc[0]) & a.zero));
-            if (++xslot == nxs) { xslot = 0; xph ^= 1u; }
-#ifdef MPSBNB_PROF
-            const long long q3 = clock64() + (long long)(__float_as_uint(acc[0]) & a.zero);
-            p_fetch += q1 - q0; p_xwait += q2 - q1; p_comp += q3 - q2;
-#endif
-            if (last) {
-                // hand the partial sums to the reducer warp; the buffer of two units ago must have been drained
+        StreamUnit un = {0, 0, 0, 0};
+        int u = (int)blockIdx.x;
+        if (u < a.nunits) un = unit_of(u);
+        while (u < a.nunits && ok && !*abort_flag) {
+            const int un_next = u + (int)gridDim.x;
+            StreamUnit nx = {0, 0, 0, 0};
+            if (un_next < a.nunits) nx = unit_of(un_next);        // in flight while this unit's stages run
+            const int nbv = lin_of(un.lin)->nbv;
+            const int qe = qb + (un.s_end - un.s_begin);
+            for (; nextq < qe; nextq += SG_GROUPS) {
+                const int s = un.s_begin + (nextq - qb);
+                const int nv0 = nbv - (s * SG_STAGE_BLOCKS + 2 * kg0);   // real-k blocks from item 0's first block on
+                if (!mbar_wait_sleep(full_bar(slot), ph, abort_flag, a.sleep_cons)) { atomicExch(&g_stream_status, 203); *abort_flag = 1; ok = false; break; }
+                const uint32_t sb = sm.addr(slot);
+                fetch_stage(wA, sb + woff[0], sb + woff[1]);
+                if (!mbar_wait_sleep(xfull_bar(xslot), xph, abort_flag, a.sleep_cons)) { atomicExch(&g_stream_status, 206); *abort_flag = 1; ok = false; break; }
+                const uint32_t xb = s_xs + (uint32_t)xslot * xs_bytes;
+#pragma unroll
+                for (int i = 0; i < SG_ITEMS; ++i) {
+                    uint32_t (&wc)[8] = (i & 1) ? wB : wA;
+                    uint32_t (&wn)[8] = (i & 1) ? wA : wB;
+                    if (i + 1 < SG_ITEMS) fetch_stage(wn, sb + woff[0] + (uint32_t)(i + 1) * ITEM_W, sb + woff[1] + (uint32_t)(i + 1) * ITEM_W);
+                    if (i + 1 == SG_ITEMS) {
+                        // the last item's bytes are needed now anyway: tie the slot's release to them
+                        const uint32_t dep = wc[7] & a.zero;
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(empty_bar(slot) + dep);
+                    }
+                    const int nvalid = nv0 - 2 * KG_STEP * i;
+                    const uint32_t ao = xb + (uint32_t)i * ITEM_A, xo = xb + (uint32_t)i * ITEM_X;
+                    if (nvalid >= 2) StageOps<XT>::stage(acc, wc, ao + aoff[0], ao + aoff[1], xo + xoff[0], xo + xoff[1], lane_word, hasx);
+                    else if (nvalid == 1) StageOps<XT>::block(acc, wc, ao + aoff[0], xo + xoff[0], lane_word, hasx);
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(xempty_bar(xslot) + (__float_as_uint(acc[0]) & a.zero));
+                slot += SG_GROUPS; if (slot >= nslots) { slot -= nslots; ph ^= 1u; }
+                xslot += SG_GROUPS; if (xslot >= nxs) { xslot -= nxs; xph ^= 1u; }
+            }
+            if (!ok) break;
+            // hand the partial sums to the reducer warp (zeros if none of this unit's stages were mine); the
+            // buffer of two units ago must have been drained
+            {
                 const int buf = uc & 1;
-                if (!mbar_wait(red_empty(buf), ((uint32_t)(uc >> 1) & 1u) ^ 1u, abort_flag)) { atomicExch(&g_stream_status, 205); *abort_flag = 1; ok = false; return; }
+                if (!mbar_wait_sleep(red_empty(buf), ((uint32_t)(uc >> 1) & 1u) ^ 1u, abort_flag, a.sleep_cons)) { atomicExch(&g_stream_status, 205); *abort_flag = 1; ok = false; break; }
                 const uint32_t rb = s_red + (uint32_t)(buf * SG_RED_BYTES);
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
@@ -622,23 +638,9 @@ __global__ void __launch_bounds__(SG_THREADS, 1) gemv4_stream_kernel(const __gri
                 __syncwarp();
                 if (lane == 0) mbar_arrive(red_full(buf));
                 ++uc;
-#ifdef MPSBNB_PROF
-                p_end += clock64() - q3;
-#endif
             }
-        };
-        // `cur` runs one stage ahead inside iterate(); track whether a stage is pending with a flag
-        bool pending = cur.valid;
-        while (pending && ok && !*abort_flag) {
-            iterate(wA, wB);
-            pending = cur.valid;
-            if (!(pending && ok)) break;
-            iterate(wB, wA);
-            pending = cur.valid;
+            qb = qe; u = un_next; un = nx;
         }
-#ifdef MPSBNB_PROF
-        if (lane == 0) { long long *pp = g_prof + (blockIdx.x * 16 + warp) * 4; pp[0] = p_fetch; pp[1] = p_xwait; pp[2] = p_comp; pp[3] = p_end; }
-#endif
     }
     // After a time-out the roles leave early while copies may still be on their way into this CTA's
     // shared memory: give them a bounded moment to land before the CTA retires.
@@ -718,6 +720,15 @@ static int fill_linear(StreamLinear &L, const HostLinear &h, int y_dtype) {
 template <typename XT>
 static int launch_stream(StreamArgs &args, cudaStream_t st, bool pdl = false) {
     args.zero = 0u;
+    {
+        static int sc = -1, so = -1;
+        if (sc < 0) {
+            int c = 32, o = 200;
+            if (const char *e = getenv("MPSBNB_STREAM_SLEEP")) sscanf(e, "%d,%d", &c, &o);
+            so = o; sc = c;
+        }
+        args.sleep_cons = (uint32_t)sc; args.sleep_other = (uint32_t)so;
+    }
     const int smem = SG_SMEM_BYTES;
     static int configured[64] = {};
     int dev = 0;

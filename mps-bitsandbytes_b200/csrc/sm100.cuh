@@ -67,6 +67,18 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     }
     return true;
 }
+// Same wait with a sleep between probes: a waiting warp that polls flat out takes issue slots from
+// the warps it is waiting for.  The abort flag and the clock are looked at every 16th probe.
+__device__ __forceinline__ bool mbar_wait_sleep(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag,
+                                                uint32_t sleep_ns, long long limit_cycles = 2000000000ll) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    for (uint32_t it = 1;; ++it) {
+        if (mbar_try_wait_suspend(bar, parity, 20000u)) return true;
+        __nanosleep(sleep_ns);
+        if ((it & 15u) == 0u && (*abort_flag != 0 || clock64() - t0 > limit_cycles)) return false;
+    }
+}
 // Alias kept for the roles off the critical path (same wait; the suspend makes a back-off loop unnecessary).
 __device__ __forceinline__ bool mbar_wait_relaxed(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag) {
     return mbar_wait(bar, parity, abort_flag);
