@@ -133,6 +133,8 @@ typedef struct mpsbnb_group_plan {
     int64_t units_offset;
     int n_linears, n_units, M, x_dtype, quant_type;
     int flags;               /* set by the caller before a run: MPSBNB_GROUP_PDL or 0 */
+    int64_t aux_offset;      /* filled by the plan call: per-CTA table inside the plan memory */
+    int grid, impl;          /* filled by the plan call: CTAs to launch, kernel family */
 } mpsbnb_group_plan;
 
 /* Launch with programmatic dependent launch: the kernel may start (build its tables, fetch

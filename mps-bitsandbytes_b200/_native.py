@@ -11,7 +11,8 @@ import re
 import torch
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "lib", "libmpsbnb_b200.so")
+# MPSBNB_B200_LIB points at a library built elsewhere (default: the in-tree build)
+LIB_PATH = os.environ.get("MPSBNB_B200_LIB") or os.path.join(_HERE, "lib", "libmpsbnb_b200.so")
 HEADER_PATH = os.path.join(_HERE, "..", "include", "mpsbnb_b200.h")
 
 F16, BF16, F32 = 0, 1, 2
@@ -33,7 +34,8 @@ class Linear4Desc(C.Structure):
 class GroupPlan(C.Structure):
     """mpsbnb_group_plan of include/mpsbnb_b200.h."""
     _fields_ = [("dev", C.c_void_p), ("units_offset", C.c_int64), ("n_linears", C.c_int), ("n_units", C.c_int),
-                ("M", C.c_int), ("x_dtype", C.c_int), ("quant_type", C.c_int), ("flags", C.c_int)]
+                ("M", C.c_int), ("x_dtype", C.c_int), ("quant_type", C.c_int), ("flags", C.c_int),
+                ("aux_offset", C.c_int64), ("grid", C.c_int), ("impl", C.c_int)]
 
 
 class NativeLibraryError(RuntimeError):

@@ -306,6 +306,9 @@ extern "C" int mpsbnb_device_status(int *status_out, int reset) {
     const int rc = stream_status_fetch(&other, reset != 0);
     if (rc != MPSBNB_OK) return rc;
     if (*status_out == 0) *status_out = other;
+    const int rc2 = tc_status_fetch(&other, reset != 0);
+    if (rc2 != MPSBNB_OK) return rc2;
+    if (*status_out == 0) *status_out = other;
     return MPSBNB_OK;
 }
 

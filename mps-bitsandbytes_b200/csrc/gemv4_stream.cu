@@ -764,6 +764,15 @@ int stream_status_fetch(int *out, bool reset) {
     return MPSBNB_OK;
 }
 
+bool decode_uses_tensor_path() {
+    static int v = -1;
+    if (v < 0) {
+        const char *e = getenv("MPSBNB_GEMV_IMPL");
+        v = (e != nullptr && strcmp(e, "tc") == 0) ? 1 : 0;
+    }
+    return v == 1;
+}
+
 // Single linear, M <= 8 (called from mpsbnb_gemv_4bit).
 int gemv4_stream_single(const void *x, int x_dtype, int64_t M, const uint8_t *packed, const void *absmax,
                         const float *absmax2, int64_t N, int64_t K, int quant_type, const void *bias, void *y,
@@ -801,7 +810,9 @@ extern "C" size_t mpsbnb_gemv_4bit_group_plan_bytes(const mpsbnb_linear4_desc *d
     if (descs == nullptr || n_linears <= 0) return 0;
     const int nu = count_units(descs, n_linears, 4);
     if (nu < 0) return 0;
-    return align_up(sizeof(StreamLinear) * (size_t)n_linears, 256) + align_up(sizeof(StreamUnit) * (size_t)nu, 256);
+    const size_t mine = align_up(sizeof(StreamLinear) * (size_t)n_linears, 256) + align_up(sizeof(StreamUnit) * (size_t)nu, 256);
+    const size_t other = tc_plan_bytes(descs, n_linears);
+    return mine > other ? mine : other;
 }
 
 extern "C" int mpsbnb_gemv_4bit_group_plan(const mpsbnb_linear4_desc *descs, int n_linears, int64_t M, int x_dtype,
@@ -811,6 +822,8 @@ extern "C" int mpsbnb_gemv_4bit_group_plan(const mpsbnb_linear4_desc *descs, int
     if (!is_16bit(x_dtype) || !valid_dtype(y_dtype) || (quant_type != MPSBNB_NF4 && quant_type != MPSBNB_FP4)) return MPSBNB_ERR_INVALID_ARG;
     if (M <= 0 || M > SG_MAX_M) return MPSBNB_ERR_UNSUPPORTED;
     if ((reinterpret_cast<uintptr_t>(plan_dev) & 255) != 0) return MPSBNB_ERR_INVALID_ARG;
+    if (decode_uses_tensor_path())
+        return tc_plan(descs, n_linears, M, x_dtype, y_dtype, quant_type, plan_dev, plan_bytes, plan_out, (cudaStream_t)stream);
     const int chunk = 4;
     const int nu = count_units(descs, n_linears, chunk);
     if (nu <= 0) return MPSBNB_ERR_INVALID_ARG;
@@ -861,11 +874,15 @@ extern "C" int mpsbnb_gemv_4bit_group_plan(const mpsbnb_linear4_desc *descs, int
     plan_out->x_dtype = x_dtype;
     plan_out->quant_type = quant_type;
     plan_out->flags = 0;
+    plan_out->aux_offset = 0;
+    plan_out->grid = 0;
+    plan_out->impl = 0;
     return MPSBNB_OK;
 }
 
 extern "C" int mpsbnb_gemv_4bit_group_run(const mpsbnb_group_plan *plan, void *stream) {
     if (plan == nullptr || plan->dev == nullptr || plan->n_units <= 0) return MPSBNB_ERR_INVALID_ARG;
+    if (plan->impl == 1) return plan->grid > 0 ? tc_run(plan, (cudaStream_t)stream) : MPSBNB_ERR_INVALID_ARG;
     StreamArgs args;
     memset(&args, 0, sizeof(args));
     args.lins = reinterpret_cast<const StreamLinear *>(plan->dev);

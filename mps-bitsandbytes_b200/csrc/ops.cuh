@@ -22,4 +22,16 @@ int gemv4_stream_single(const void *x, int x_dtype, int64_t M, const uint8_t *pa
                         int y_dtype, cudaStream_t st);
 int stream_status_fetch(int *out, bool reset);
 
+// tensor-path decode kernel (gemv4_tc.cu)
+int gemv4_tc_single(const void *x, int x_dtype, int64_t M, const uint8_t *packed, const void *absmax,
+                    const float *absmax2, int64_t N, int64_t K, int quant_type, const void *bias, void *y,
+                    int y_dtype, cudaStream_t st);
+size_t tc_plan_bytes(const mpsbnb_linear4_desc *descs, int n_linears);
+int tc_plan(const mpsbnb_linear4_desc *descs, int n_linears, int64_t M, int x_dtype, int y_dtype, int quant_type,
+            void *plan_dev, size_t plan_bytes, mpsbnb_group_plan *plan_out, cudaStream_t st);
+int tc_run(const mpsbnb_group_plan *plan, cudaStream_t st);
+int tc_status_fetch(int *out, bool reset);
+// true when the environment selects the tcgen05 decode kernel (MPSBNB_GEMV_IMPL=tc)
+bool decode_uses_tensor_path();
+
 }  // namespace mpsbnb
