@@ -34,6 +34,7 @@
 #include "sm100.cuh"
 
 #include <stdlib.h>
+#include <type_traits>
 #include <string.h>
 
 namespace mpsbnb {
@@ -58,12 +59,6 @@ constexpr int SG_MAX_M = 8;
 // status word of this translation unit (device code is not linked relocatably); read by
 // stream_status_fetch() on behalf of mpsbnb_device_status()
 static __device__ int g_stream_status = 0;
-#ifdef MPSBNB_PROF
-static __device__ long long g_prof[148 * 16 * 4];
-#define PROF_T(v) const long long v = clock64()
-#else
-#define PROF_T(v)
-#endif
 
 
 struct StreamLinear {
@@ -246,6 +241,68 @@ template <> struct StageOps<__nv_bfloat16> {
                                                  uint32_t lw, uint32_t hasx) { MPSBNB_BLOCK_ASM("bf16"); }
 };
 
+// ---- batch <= 2: plain dot products instead of tensor-core MMAs.
+// With one or two batch rows an MMA spends 7/8 of its columns on padding and, worse, its issue cost sits on
+// the critical path of the warp that also has to issue the table loads.  Here a LANE owns a weight ROW: it
+// reads the 32 packed bytes of its row for one block, looks every byte up (same byte-permute + table load)
+// and multiplies the two codes with the two x values by mixed-precision FMAs (fp16 x fp16 + fp32 -> fp32,
+// exact products, fp32 accumulation).  x is the same for all lanes, so its loads are broadcasts.
+constexpr int SG_DOT_MAX_M = 2;
+__device__ __forceinline__ uint4 lds128v(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
+    return v;
+}
+__device__ __forceinline__ float lds_f32v(uint32_t addr) { float v; asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory"); return v; }
+// the table never changes after the prologue: the compiler may schedule this load freely
+__device__ __forceinline__ uint32_t lut_pair(uint32_t addr) { uint32_t v; asm("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr)); return v; }
+// acc += lo(w) * lo(x) + hi(w) * hi(x), both products exact, accumulated in fp32
+template <typename XT> __device__ __forceinline__ void fma_pair(float &acc, uint32_t w, uint32_t x);
+template <> __device__ __forceinline__ void fma_pair<__half>(float &acc, uint32_t w, uint32_t x) {
+    asm("{\n\t.reg .b16 wl, wh, xl, xh;\n\tmov.b32 {wl, wh}, %1;\n\tmov.b32 {xl, xh}, %2;\n\t"
+        "fma.rn.f32.f16 %0, wl, xl, %0;\n\tfma.rn.f32.f16 %0, wh, xh, %0;\n\t}\n" : "+f"(acc) : "r"(w), "r"(x));
+}
+template <> __device__ __forceinline__ void fma_pair<__nv_bfloat16>(float &acc, uint32_t w, uint32_t x) {
+    asm("{\n\t.reg .b16 wl, wh, xl, xh;\n\tmov.b32 {wl, wh}, %1;\n\tmov.b32 {xl, xh}, %2;\n\t"
+        "fma.rn.f32.bf16 %0, wl, xl, %0;\n\tfma.rn.f32.bf16 %0, wh, xh, %0;\n\t}\n" : "+f"(acc) : "r"(w), "r"(x));
+}
+// one block (64 k) of this lane's row against NM batch rows; w[0..7] = the row's 32 packed bytes
+template <typename XT, int NM>
+__device__ __forceinline__ void dot_block(float (&tot)[SG_DOT_MAX_M], const uint32_t (&w)[8], float scale, uint32_t xa, uint32_t lw) {
+    float p[NM][4];
+#pragma unroll
+    for (int m = 0; m < NM; ++m)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) p[m][e] = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        uint4 xv[NM];
+#pragma unroll
+        for (int m = 0; m < NM; ++m) xv[m] = lds128v(xa + (uint32_t)(m * SG_XPITCH + 16 * i));   // k = 8 i .. 8 i + 7, same for all lanes
+        const uint32_t c0 = lut_pair(__byte_perm(w[i], lw, 0x7604));
+        const uint32_t c1 = lut_pair(__byte_perm(w[i], lw, 0x7614));
+        const uint32_t c2 = lut_pair(__byte_perm(w[i], lw, 0x7624));
+        const uint32_t c3 = lut_pair(__byte_perm(w[i], lw, 0x7634));
+#pragma unroll
+        for (int m = 0; m < NM; ++m) {
+            fma_pair<XT>(p[m][0], c0, xv[m].x);
+            fma_pair<XT>(p[m][1], c1, xv[m].y);
+            fma_pair<XT>(p[m][2], c2, xv[m].z);
+            fma_pair<XT>(p[m][3], c3, xv[m].w);
+        }
+    }
+#pragma unroll
+    for (int m = 0; m < NM; ++m) tot[m] = fmaf(scale, (p[m][0] + p[m][1]) + (p[m][2] + p[m][3]), tot[m]);
+}
+__device__ __forceinline__ void fetch_row_block(uint32_t (&w)[8], uint32_t a0, uint32_t a1) {
+    asm volatile(
+        "ld.shared.v4.u32 {%0, %1, %2, %3}, [%8];\n\t"
+        "ld.shared.v4.u32 {%4, %5, %6, %7}, [%9];\n\t"
+        : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]), "=r"(w[4]), "=r"(w[5]), "=r"(w[6]), "=r"(w[7])
+        : "r"(a0), "r"(a1)
+        : "memory");
+}
+
 // Shared-memory map, in ABSOLUTE shared-window addresses.  The code-pair table sits at exactly
 // 128 KiB so that "table + byte * 256 + lane * 4" is one byte-permute of (weight word, lane word):
 // byte 0 = lane * 4, byte 1 = the weight byte, byte 2 = 0x02 — no addition.  Below it: partial
@@ -279,6 +336,7 @@ __global__ void __launch_bounds__(SG_THREADS, 1) gemv4_stream_kernel(const __gri
     // full[8] empty[8] red_full[2] red_empty[2] xfull[8] xempty[8] (288 B), abort flag, 32 zero bytes at +320
     const uint32_t s_bar = s_base + 2 * SG_RED_BYTES;
     const uint32_t s_zero = s_bar + 320u;
+
     const int nxs = a.M <= 2 ? SG_MAX_XS : 4;                        // scale/x slots (released after the MMAs)
     const uint32_t xs_bytes = (uint32_t)(SG_A_BYTES + ((a.M * SG_XPITCH + 127) / 128) * 128);
     const uint32_t s_xs = (s_bar + 384u + 127u) & ~127u;
@@ -359,12 +417,6 @@ __global__ void __launch_bounds__(SG_THREADS, 1) gemv4_stream_kernel(const __gri
                 for (int s = un.s_begin; s < un.s_end; ++s) {
                     if (!mbar_wait_sleep(empty_bar(slot), ph ^ 1u, abort_flag, a.sleep_other)) { atomicExch(&g_stream_status, 201); *abort_flag = 1; ok = false; break; }
                     const uint32_t bar = full_bar(slot), dst = sm.addr(slot);
-#ifdef MPSBNB_SELFCHECK
-                    if ((dst & 1023u) || dst + SG_W_BYTES > s_base + SG_SMEM_BYTES || (dst < SG_LUT_ABS && dst + SG_W_BYTES > SG_LUT_ABS) ||
-                        dst < sm.low0 || un.row0 < 0 || un.row0 >= L->N || s < 0) {
-                        atomicExch(&g_stream_status, 304); *abort_flag = 1; ok = false; break;
-                    }
-#endif
                     mbar_arrive_expect_tx(bar, SG_W_BYTES);
                     if (m3) {
                         tma_load_3d(dst, map, bar, 0, un.row0, s * 4);
@@ -395,8 +447,14 @@ __global__ void __launch_bounds__(SG_THREADS, 1) gemv4_stream_kernel(const __gri
             const int n = un.row0 + lane;
             for (int m = 0; m < a.M; ++m) {
                 float sum = 0.0f;
+                if (a.M <= SG_DOT_MAX_M) {
+                    // dot-product path: [warp][m][row] partial sums of all 16 warps
 #pragma unroll
-                for (int k8 = 0; k8 < 8; ++k8) sum += red[((k8 * 2 + wrt) * 8 + m) * 20 + i];
+                    for (int w16 = 0; w16 < SG_CONSUMERS; ++w16) sum += red[(w16 * SG_DOT_MAX_M + m) * 32 + lane];
+                } else {
+#pragma unroll
+                    for (int k8 = 0; k8 < 8; ++k8) sum += red[((k8 * 2 + wrt) * 8 + m) * 20 + i];
+                }
                 if (n < L->N) {
                     if (L->bias != nullptr && un.s_begin == 0) sum += to_f32<XT>(reinterpret_cast<const XT *>(L->bias)[n]);
                     const int64_t o = (int64_t)m * L->N + n;
@@ -509,16 +567,6 @@ __global__ void __launch_bounds__(SG_THREADS, 1) gemv4_stream_kernel(const __gri
                         mbar_arrive_expect_tx(xfull_bar(my_x), nb2 * (uint32_t)a.M);
                         const int col = (my_s * (SG_STAGE_BLOCKS * 64)) % my_L->x_period;
                         const unsigned char *src = reinterpret_cast<const unsigned char *>(my_L->x) + (int64_t)col * 2;
-#ifdef MPSBNB_SELFCHECK
-                        {
-                            const uint32_t d0 = xb + SG_A_BYTES, d1 = xb + SG_A_BYTES + (a.M - 1) * SG_XPITCH + nb2;
-                            if ((nb2 & 15u) || (d0 & 15u) || (reinterpret_cast<uintptr_t>(src) & 15) || ((my_L->x_ld * 2) & 15) ||
-                                d1 > xb + xs_bytes || xb + xs_bytes > sm.low0 || xcols < 0) {
-                                atomicExch(&g_stream_status, 301); *abort_flag = 1;
-                            }
-                        }
-                        if (*abort_flag) break;
-#endif
                         if (nb2 != 0u)
                             for (int m = 0; m < a.M; ++m)
                                 bulk_load_1d(xb + SG_A_BYTES + m * SG_XPITCH, src + (int64_t)m * my_L->x_ld * 2, nb2, xfull_bar(my_x));
@@ -577,69 +625,125 @@ __global__ void __launch_bounds__(SG_THREADS, 1) gemv4_stream_kernel(const __gri
         constexpr uint32_t ITEM_W = (uint32_t)(KG_STEP * 2 * 1024);   // 2 blocks = half a 4 KiB box
         constexpr uint32_t ITEM_X = (uint32_t)(KG_STEP * 2 * 64 * 2); // x bytes per block pair step
         constexpr uint32_t ITEM_A = (uint32_t)(KG_STEP * 2 * 32 * 4); // scale bytes per block pair step
+        const bool dot = a.M <= SG_DOT_MAX_M;                    // lane = row, one block per item (see dot_block)
+        if (dot) {
+            woff[0] = (uint32_t)(lane * 128 + (((2 * j) ^ (lane & 7)) << 4));
+            woff[1] = (uint32_t)(lane * 128 + (((2 * j + 1) ^ (lane & 7)) << 4));
+            xoff[0] = (uint32_t)(SG_A_BYTES + j * 128);
+            aoff[0] = (uint32_t)((j * 32 + lane) * 4);
+        }
+        static_assert(SG_GROUP_WARPS == 4 && SG_ITEMS == 4, "the dot path deals the 16 blocks of a stage to 4 warps, box by box");
         const uint32_t hasx = g < a.M ? 1u : 0u;
-        int slot = grp % nslots, xslot = grp % nxs;              // ring positions of my next stage
-        uint32_t ph = (uint32_t)(grp / nslots) & 1u, xph = (uint32_t)(grp / nxs) & 1u;
-        int nextq = grp;                                          // my next stage in the CTA's stage sequence
-        int qb = 0, uc = 0;
-        float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-        bool ok = true;
         uint32_t wA[8], wB[8];
-        StreamUnit un = {0, 0, 0, 0};
-        int u = (int)blockIdx.x;
-        if (u < a.nunits) un = unit_of(u);
-        while (u < a.nunits && ok && !*abort_flag) {
-            const int un_next = u + (int)gridDim.x;
-            StreamUnit nx = {0, 0, 0, 0};
-            if (un_next < a.nunits) nx = unit_of(un_next);        // in flight while this unit's stages run
-            const int nbv = lin_of(un.lin)->nbv;
-            const int qe = qb + (un.s_end - un.s_begin);
-            for (; nextq < qe; nextq += SG_GROUPS) {
-                const int s = un.s_begin + (nextq - qb);
+
+        // The walk over this warp's stages, shared by the compute variants below.  stage_fn(s, nbv, sb, xb, ebar)
+        // does one stage (and arrives on ebar, the weight slot's "empty" barrier, once its bytes are in
+        // registers); it returns a word that depends on its last result.  flush_fn(rb) stores the unit's partial
+        // sums into the reducer's buffer and clears them.  Only ONE variant runs in a launch, so only its code
+        // is resident in the instruction caches.
+        auto run_units = [&](auto &&stage_fn, auto &&flush_fn) {
+            int slot = grp % nslots, xslot = grp % nxs;              // ring positions of my next stage
+            uint32_t ph = (uint32_t)(grp / nslots) & 1u, xph = (uint32_t)(grp / nxs) & 1u;
+            int nextq = grp;                                          // my next stage in the CTA's stage sequence
+            int qb = 0, uc = 0;
+            bool ok = true;
+            StreamUnit un = {0, 0, 0, 0};
+            int u = (int)blockIdx.x;
+            if (u < a.nunits) un = unit_of(u);
+            while (u < a.nunits && ok && !*abort_flag) {
+                const int un_next = u + (int)gridDim.x;
+                StreamUnit nx = {0, 0, 0, 0};
+                if (un_next < a.nunits) nx = unit_of(un_next);        // in flight while this unit's stages run
+                const int nbv = lin_of(un.lin)->nbv;
+                const int qe = qb + (un.s_end - un.s_begin);
+#pragma unroll 1
+                for (; nextq < qe; nextq += SG_GROUPS) {
+                    const int s = un.s_begin + (nextq - qb);
+                    if (!mbar_wait_sleep(full_bar(slot), ph, abort_flag, a.sleep_cons)) { atomicExch(&g_stream_status, 203); *abort_flag = 1; ok = false; break; }
+                    if (!mbar_wait_sleep(xfull_bar(xslot), xph, abort_flag, a.sleep_cons)) { atomicExch(&g_stream_status, 206); *abort_flag = 1; ok = false; break; }
+                    const uint32_t dep = stage_fn(s, nbv, sm.addr(slot), s_xs + (uint32_t)xslot * xs_bytes, empty_bar(slot));
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(xempty_bar(xslot) + (dep & a.zero));
+                    slot += SG_GROUPS; if (slot >= nslots) { slot -= nslots; ph ^= 1u; }
+                    xslot += SG_GROUPS; if (xslot >= nxs) { xslot -= nxs; xph ^= 1u; }
+                }
+                if (!ok) break;
+                // hand the partial sums to the reducer warp (zeros if none of this unit's stages were mine); the
+                // buffer of two units ago must have been drained
+                const int buf = uc & 1;
+                if (!mbar_wait_sleep(red_empty(buf), ((uint32_t)(uc >> 1) & 1u) ^ 1u, abort_flag, a.sleep_cons)) { atomicExch(&g_stream_status, 205); *abort_flag = 1; break; }
+                flush_fn(s_red + (uint32_t)(buf * SG_RED_BYTES));
+                __syncwarp();
+                if (lane == 0) mbar_arrive(red_full(buf));
+                ++uc;
+                qb = qe; u = un_next; un = nx;
+            }
+        };
+        // hands the weight slot back; `last` is a register filled by the slot's last load
+        auto release_slot = [&](uint32_t ebar, uint32_t last) {
+            const uint32_t dep = last & a.zero;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(ebar + dep);
+        };
+
+        if (!dot) {
+            // ---- batch 3 .. 8: tensor-core MMAs, two blocks x 16 rows per item
+            float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            auto stage_mma = [&](int s, int nbv, uint32_t sb, uint32_t xb, uint32_t ebar) -> uint32_t {
                 const int nv0 = nbv - (s * SG_STAGE_BLOCKS + 2 * kg0);   // real-k blocks from item 0's first block on
-                if (!mbar_wait_sleep(full_bar(slot), ph, abort_flag, a.sleep_cons)) { atomicExch(&g_stream_status, 203); *abort_flag = 1; ok = false; break; }
-                const uint32_t sb = sm.addr(slot);
                 fetch_stage(wA, sb + woff[0], sb + woff[1]);
-                if (!mbar_wait_sleep(xfull_bar(xslot), xph, abort_flag, a.sleep_cons)) { atomicExch(&g_stream_status, 206); *abort_flag = 1; ok = false; break; }
-                const uint32_t xb = s_xs + (uint32_t)xslot * xs_bytes;
 #pragma unroll
                 for (int i = 0; i < SG_ITEMS; ++i) {
                     uint32_t (&wc)[8] = (i & 1) ? wB : wA;
                     uint32_t (&wn)[8] = (i & 1) ? wA : wB;
                     if (i + 1 < SG_ITEMS) fetch_stage(wn, sb + woff[0] + (uint32_t)(i + 1) * ITEM_W, sb + woff[1] + (uint32_t)(i + 1) * ITEM_W);
-                    if (i + 1 == SG_ITEMS) {
-                        // the last item's bytes are needed now anyway: tie the slot's release to them
-                        const uint32_t dep = wc[7] & a.zero;
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(empty_bar(slot) + dep);
-                    }
+                    if (i + 1 == SG_ITEMS) release_slot(ebar, wc[7]);     // the last item's bytes are needed now anyway
                     const int nvalid = nv0 - 2 * KG_STEP * i;
                     const uint32_t ao = xb + (uint32_t)i * ITEM_A, xo = xb + (uint32_t)i * ITEM_X;
                     if (nvalid >= 2) StageOps<XT>::stage(acc, wc, ao + aoff[0], ao + aoff[1], xo + xoff[0], xo + xoff[1], lane_word, hasx);
                     else if (nvalid == 1) StageOps<XT>::block(acc, wc, ao + aoff[0], xo + xoff[0], lane_word, hasx);
                 }
-                __syncwarp();
-                if (lane == 0) mbar_arrive(xempty_bar(xslot) + (__float_as_uint(acc[0]) & a.zero));
-                slot += SG_GROUPS; if (slot >= nslots) { slot -= nslots; ph ^= 1u; }
-                xslot += SG_GROUPS; if (xslot >= nxs) { xslot -= nxs; xph ^= 1u; }
-            }
-            if (!ok) break;
-            // hand the partial sums to the reducer warp (zeros if none of this unit's stages were mine); the
-            // buffer of two units ago must have been drained
-            {
-                const int buf = uc & 1;
-                if (!mbar_wait_sleep(red_empty(buf), ((uint32_t)(uc >> 1) & 1u) ^ 1u, abort_flag, a.sleep_cons)) { atomicExch(&g_stream_status, 205); *abort_flag = 1; ok = false; break; }
-                const uint32_t rb = s_red + (uint32_t)(buf * SG_RED_BYTES);
+                return __float_as_uint(acc[0]);
+            };
+            auto flush_mma = [&](uint32_t rb) {
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
                     sts_f32(rb + (uint32_t)(((warp * 8 + 2 * t + (c & 1)) * 20 + g + 8 * (c >> 1)) * 4), acc[c]);
                     acc[c] = 0.0f;
                 }
-                __syncwarp();
-                if (lane == 0) mbar_arrive(red_full(buf));
-                ++uc;
-            }
-            qb = qe; u = un_next; un = nx;
+            };
+            run_units(stage_mma, flush_mma);
+        } else {
+            // ---- batch 1 and 2: dot products, one block x 32 rows per item, two items per loop trip
+            float tot[SG_DOT_MAX_M] = {0.0f, 0.0f};
+            auto flush_dot = [&](uint32_t rb) {
+#pragma unroll
+                for (int m = 0; m < SG_DOT_MAX_M; ++m) {
+                    sts_f32(rb + (uint32_t)(((warp * SG_DOT_MAX_M + m) * 32 + lane) * 4), tot[m]);
+                    tot[m] = 0.0f;
+                }
+            };
+            auto stage_dot = [&](auto nm_tag, int s, int nbv, uint32_t sb, uint32_t xb, uint32_t ebar) -> uint32_t {
+                constexpr int NM = decltype(nm_tag)::value;
+                const int nvd = nbv - (s * SG_STAGE_BLOCKS + j);          // real-k blocks from my first block on, in steps of 4
+                const uint32_t w0 = sb + woff[0], w1 = sb + woff[1];
+                const uint32_t xx = xb + xoff[0];
+                const uint32_t ab = xb + aoff[0];                     // my row's scale of block j + 4 i: fp32 [block][row]
+                fetch_row_block(wA, w0, w1);
+#pragma unroll 1
+                for (int i = 0; i < SG_ITEMS; i += 2) {
+                    fetch_row_block(wB, w0 + (uint32_t)(i + 1) * ITEM_W, w1 + (uint32_t)(i + 1) * ITEM_W);
+                    if (nvd - 4 * i >= 1) dot_block<XT, NM>(tot, wA, lds_f32v(ab + (uint32_t)i * ITEM_A), xx + (uint32_t)i * ITEM_X, lane_word);
+                    if (i + 2 < SG_ITEMS) fetch_row_block(wA, w0 + (uint32_t)(i + 2) * ITEM_W, w1 + (uint32_t)(i + 2) * ITEM_W);
+                    else release_slot(ebar, wB[7]);
+                    if (nvd - 4 * (i + 1) >= 1) dot_block<XT, NM>(tot, wB, lds_f32v(ab + (uint32_t)(i + 1) * ITEM_A), xx + (uint32_t)(i + 1) * ITEM_X, lane_word);
+                }
+                return __float_as_uint(tot[0]);
+            };
+            if (a.M == 1)
+                run_units([&](int s, int nbv, uint32_t sb, uint32_t xb, uint32_t ebar) { return stage_dot(std::integral_constant<int, 1>{}, s, nbv, sb, xb, ebar); }, flush_dot);
+            else
+                run_units([&](int s, int nbv, uint32_t sb, uint32_t xb, uint32_t ebar) { return stage_dot(std::integral_constant<int, 2>{}, s, nbv, sb, xb, ebar); }, flush_dot);
         }
     }
     // After a time-out the roles leave early while copies may still be on their way into this CTA's
@@ -706,10 +810,10 @@ static int fill_linear(StreamLinear &L, const HostLinear &h, int y_dtype) {
                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     }
     if (cr != CUDA_SUCCESS) return MPSBNB_ERR_INVALID_ARG;
-    L.pad_ = 0;
     L.x = h.x; L.absmax = h.absmax; L.absmax2 = h.absmax2; L.bias = h.bias; L.y = h.y; L.acc = h.acc;
     L.x_ld = h.x_ld;
     L.N = (int)h.N; L.K = (int)h.K; L.nb = (int)(Kp / 64); L.nbv = (int)((h.K + 63) / 64);
+    L.pad_ = 0;
     L.x_period = (int)(h.x_period > 0 ? h.x_period : h.K);
     L.y_dtype = y_dtype;
     L.x_vec_ok = (h.x_ld % 8 == 0) && (L.x_period % 8 == 0) && (h.K % 8 == 0) && aligned16(h.x);
@@ -720,15 +824,7 @@ static int fill_linear(StreamLinear &L, const HostLinear &h, int y_dtype) {
 template <typename XT>
 static int launch_stream(StreamArgs &args, cudaStream_t st, bool pdl = false) {
     args.zero = 0u;
-    {
-        static int sc = -1, so = -1;
-        if (sc < 0) {
-            int c = 32, o = 200;
-            if (const char *e = getenv("MPSBNB_STREAM_SLEEP")) sscanf(e, "%d,%d", &c, &o);
-            so = o; sc = c;
-        }
-        args.sleep_cons = (uint32_t)sc; args.sleep_other = (uint32_t)so;
-    }
+    args.sleep_cons = 32u; args.sleep_other = 200u;
     const int smem = SG_SMEM_BYTES;
     static int configured[64] = {};
     int dev = 0;
@@ -750,11 +846,6 @@ static int launch_stream(StreamArgs &args, cudaStream_t st, bool pdl = false) {
     return check_launch();
 }
 
-#ifdef MPSBNB_PROF
-}  // namespace mpsbnb
-extern "C" int mpsbnb_debug_prof(long long *out) { return cudaMemcpyFromSymbol(out, mpsbnb::g_prof, sizeof(long long) * 148 * 16 * 4) == cudaSuccess ? 0 : -3; }
-namespace mpsbnb {
-#endif
 int stream_status_fetch(int *out, bool reset) {
     MPSBNB_CUDA_TRY(cudaMemcpyFromSymbol(out, g_stream_status, sizeof(int)));
     if (reset) {
@@ -764,13 +855,19 @@ int stream_status_fetch(int *out, bool reset) {
     return MPSBNB_OK;
 }
 
+// 0: TMA ring + mma.sync / dot products (default); 1: TMA ring + tcgen05 with the expanded weights in tensor memory
+static int g_decode_kernel = -1;
 bool decode_uses_tensor_path() {
-    static int v = -1;
-    if (v < 0) {
+    if (g_decode_kernel < 0) {
         const char *e = getenv("MPSBNB_GEMV_IMPL");
-        v = (e != nullptr && strcmp(e, "tc") == 0) ? 1 : 0;
+        g_decode_kernel = (e != nullptr && strcmp(e, "tc") == 0) ? 1 : 0;
     }
-    return v == 1;
+    return g_decode_kernel == 1;
+}
+int decode_kernel_select(int which) {
+    const int old = decode_uses_tensor_path() ? 1 : 0;
+    if (which == 0 || which == 1) g_decode_kernel = which;
+    return old;
 }
 
 // Single linear, M <= 8 (called from mpsbnb_gemv_4bit).
@@ -790,6 +887,8 @@ int gemv4_stream_single(const void *x, int x_dtype, int64_t M, const uint8_t *pa
 }  // namespace mpsbnb
 
 using namespace mpsbnb;
+
+extern "C" int mpsbnb_decode_kernel_select(int which) { return decode_kernel_select(which); }
 
 // ------------------------------------------------------------------------------------------
 // grouped launches: a plan (device memory supplied by the caller) holds the linears and units

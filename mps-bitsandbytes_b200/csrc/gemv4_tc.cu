@@ -44,7 +44,7 @@ constexpr int TG_STAGE_BLOCKS = 4;                         // quantisation block
 constexpr int TG_STAGE_K = TG_STAGE_BLOCKS * 64;
 constexpr int TG_W_BYTES = TG_ROWS * TG_STAGE_K / 2;       // 16384
 constexpr int TG_X_BYTES = TG_N * TG_STAGE_K * 2;          // 8192: four [16 x 64] atoms of 2048 B
-constexpr int TG_A_BYTES = TG_STAGE_BLOCKS * TG_ROWS * 4;  // 2048: fp32 scale [block][row]
+constexpr int TG_A_BYTES = TG_STAGE_BLOCKS * TG_ROWS * 4;  // 2048: fp32 scale [row][block], or int8 codes [row] + fp32 maxima [row]
 constexpr int TG_XS_BYTES = TG_X_BYTES + TG_A_BYTES;
 constexpr int TG_NXS = 4;                                  // scale/x slots (a multiple of TG_LOADERS: one loader per slot)
 constexpr int TG_MAX_SLOTS = 9;
@@ -73,7 +73,8 @@ struct TcLinear {
     int x_period;             // x column = k mod x_period (x_period >= K: plain)
     int y_dtype;
     int x_vec_ok;             // 16-byte loads of x are legal and never straddle K or the period
-    int pad0, pad1;
+    int scale_async;          // every stage's scales of a row are one aligned, complete group of four: async copies
+    int pad1;
 };
 
 struct __align__(16) TcPiece { int lin, row0, s_begin, s_end, parts, pad0, pad1, pad2; };   // parts: pieces of this tile (1 = whole)
@@ -107,7 +108,19 @@ __device__ __forceinline__ uint4 tg_lds128(uint32_t addr) {
     asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
     return v;
 }
+__device__ __forceinline__ uint32_t tg_lds_u32(uint32_t addr) { uint32_t v; asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory"); return v; }
 __device__ __forceinline__ float tg_lds_f32(uint32_t addr) { float v; asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory"); return v; }
+// Ampere-style asynchronous copies global -> shared (4 or 16 bytes per thread); `bytes_valid` < 16 zero-fills.
+__device__ __forceinline__ void tg_cp_async4(uint32_t dst, const void *src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void tg_cp_async16(uint32_t dst, const void *src, uint32_t bytes_valid) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes_valid) : "memory");
+}
+// one arrival on `bar` once all asynchronous copies this thread has issued so far have landed
+__device__ __forceinline__ void tg_cp_async_arrive(uint32_t bar) {
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
+}
 // table load: the table never changes after the prologue, so the compiler may move this freely
 __device__ __forceinline__ uint32_t tg_lut(uint32_t addr) { uint32_t v; asm("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr)); return v; }
 
@@ -136,6 +149,8 @@ __global__ void __launch_bounds__(TG_THREADS, 1) gemv4_tc_kernel(const __grid_co
     auto dempty_bar = [&](int s) { return s_bar + 8u * (2 * TG_MAX_SLOTS + 2 * TG_NXS + 2 * TG_ABUFS + 2 + s); };
     static_assert(8 * (2 * TG_MAX_SLOTS + 2 * TG_NXS + 2 * TG_ABUFS + 4) <= 320, "barrier area");
     const uint32_t s_holder = s_bar + 320u;
+    const uint32_t s_mode = s_bar + 336u;                             // per scale/x slot: 1 = raw int8 scales + second-level maxima
+
     const uint32_t s_xs = (s_bar + 512u + 1023u) & ~1023u;            // scale/x ring: [x tile 8 KiB][scales 2 KiB] per slot
     TgSlots sm;
     sm.low0 = s_xs + (uint32_t)(TG_NXS * TG_XS_BYTES);
@@ -157,7 +172,7 @@ __global__ void __launch_bounds__(TG_THREADS, 1) gemv4_tc_kernel(const __grid_co
 
     if (tid == 0) {
         for (int s = 0; s < nslots; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), TG_CONSUMERS); }
-        for (int s = 0; s < TG_NXS; ++s) { mbar_init(xfull_bar(s), 1); mbar_init(xempty_bar(s), TG_CONSUMERS + 1); }
+        for (int s = 0; s < TG_NXS; ++s) { mbar_init(xfull_bar(s), 32); mbar_init(xempty_bar(s), TG_CONSUMERS + 1); }
         for (int s = 0; s < TG_ABUFS; ++s) { mbar_init(afull_bar(s), TG_CONSUMERS); mbar_init(aempty_bar(s), 1); }
         for (int s = 0; s < 2; ++s) { mbar_init(dfull_bar(s), 1); mbar_init(dempty_bar(s), 4); }
         *abort_flag = 0;
@@ -233,6 +248,7 @@ __global__ void __launch_bounds__(TG_THREADS, 1) gemv4_tc_kernel(const __grid_co
                     if (!mbar_wait_sleep(xfull_bar(xslot), xph, abort_flag, kSleepFast)) { atomicExch(&g_tc_status, 403); *abort_flag = 1; ok = false; break; }
                     if (!mbar_wait_sleep(afull_bar(abuf), aph, abort_flag, kSleepFast)) { atomicExch(&g_tc_status, 404); *abort_flag = 1; ok = false; break; }
                     tc_fence_after();
+                    fence_proxy_async_smem();                            // the x tile was written through the generic proxy
                     const uint64_t xdesc = umma_desc_k_sw128(s_xs + (uint32_t)(xslot * TG_XS_BYTES));
                     const uint32_t tmem_a = tmem_base + (uint32_t)(abuf * 128);
 #pragma unroll
@@ -387,42 +403,67 @@ __global__ void __launch_bounds__(TG_THREADS, 1) gemv4_tc_kernel(const __grid_co
             }
         };
         float cur[16];
-        uint4 xcur[2];
         bool more = advance_to_mine();
-        const bool xpre = a.M <= 2;                                      // x of the next stage is prefetched too
-        if (more) {
-            read_scales(L, pc.row0, s, cur);
-            if (xpre) for (int m = 0; m < a.M; ++m) xcur[m] = read_x(L, s, m);
-        }
+        if (more && !L->scale_async) read_scales(L, pc.row0, s, cur);
         while (more && !*abort_flag) {
-            const int my_x = xslot, my_s = s;
+            const int my_x = xslot, my_s = s, my_row0 = pc.row0;
             const uint32_t my_ph = xph;
             const TcLinear *my_L = L;
+            const bool my_async = my_L->scale_async != 0;
             step();
             float nxt[16];
-            uint4 xnxt[2];
             more = advance_to_mine();
-            if (more) {
-                read_scales(L, pc.row0, s, nxt);
-                if (xpre) for (int m = 0; m < a.M; ++m) xnxt[m] = read_x(L, s, m);
-            }
+            if (more && !L->scale_async) read_scales(L, pc.row0, s, nxt);
             if (!mbar_wait_sleep(xempty_bar(my_x), my_ph ^ 1u, abort_flag, kSleepSlow)) { atomicExch(&g_tc_status, 406); *abort_flag = 1; break; }
             const uint32_t xb = s_xs + (uint32_t)(my_x * TG_XS_BYTES);
+            const uint32_t ab = xb + TG_X_BYTES;
+            if (my_async) {
+                // scales: nothing passes through registers, so this warp never waits for global memory and runs
+                // as far ahead as the ring allows.  Row n gets its four codes (or floats) and its second-level maximum.
+                const int b0 = my_s * TG_STAGE_BLOCKS;
 #pragma unroll
-            for (int i = 0; i < 4; ++i)
+                for (int i = 0; i < 4; ++i) {
+                    const int rr = lane + 32 * i;
+                    const int n = my_row0 + rr;
+                    if (n < my_L->N) {
+                        const int64_t i0 = (int64_t)n * my_L->nb + b0;
+                        if (my_L->absmax2 != nullptr) {
+                            tg_cp_async4(ab + (uint32_t)(rr * 4), reinterpret_cast<const int8_t *>(my_L->absmax) + i0);
+                            tg_cp_async4(ab + 512u + (uint32_t)(rr * 4), my_L->absmax2 + (i0 >> 8));
+                        } else {
+                            tg_cp_async16(ab + (uint32_t)(rr * 16), reinterpret_cast<const float *>(my_L->absmax) + i0, 16u);
+                        }
+                    } else if (my_L->absmax2 != nullptr) {
+                        tg_sts32(ab + (uint32_t)(rr * 4), 0u);
+                        tg_sts_f32(ab + 512u + (uint32_t)(rr * 4), 0.0f);
+                    } else {
+                        tg_sts128(ab + (uint32_t)(rr * 16), make_uint4(0u, 0u, 0u, 0u));
+                    }
+                }
+                if (lane == 0) tg_sts32(s_mode + 4u * my_x, my_L->absmax2 != nullptr ? 1u : 0u);
+            } else {
 #pragma unroll
-                for (int j = 0; j < 4; ++j) tg_sts_f32(xb + TG_X_BYTES + (uint32_t)((j * TG_ROWS + lane + 32 * i) * 4), cur[4 * i + j]);
+                for (int i = 0; i < 4; ++i)
+                    tg_sts128(ab + (uint32_t)((lane + 32 * i) * 16),
+                              make_uint4(__float_as_uint(cur[4 * i]), __float_as_uint(cur[4 * i + 1]), __float_as_uint(cur[4 * i + 2]), __float_as_uint(cur[4 * i + 3])));
+                if (lane == 0) tg_sts32(s_mode + 4u * my_x, 0u);
+            }
             // x tile: row m of atom (lane >> 3), 16-byte chunk (lane & 7) ^ m  (128-byte swizzle)
             for (int m = 0; m < a.M; ++m) {
-                const uint4 v = xpre ? xcur[m] : read_x(my_L, my_s, m);
-                tg_sts128(xb + (uint32_t)((lane >> 3) * 2048 + m * 128 + (((lane & 7) ^ m) << 4)), v);
+                const uint32_t dst = xb + (uint32_t)((lane >> 3) * 2048 + m * 128 + (((lane & 7) ^ m) << 4));
+                if (my_L->x_vec_ok) {
+                    const int k0 = my_s * TG_STAGE_K + lane * 8;
+                    const bool in = k0 < my_L->K;
+                    const XT *xr = reinterpret_cast<const XT *>(my_L->x) + (int64_t)m * my_L->x_ld;
+                    tg_cp_async16(dst, xr + (in ? k0 % my_L->x_period : 0), in ? 16u : 0u);
+                } else {
+                    tg_sts128(dst, read_x(my_L, my_s, m));
+                }
             }
-            fence_proxy_async_smem();                                    // the MMA reads the tile through the async proxy
-            __syncwarp();
-            if (lane == 0) mbar_arrive(xfull_bar(my_x));
+            fence_proxy_async_smem();
+            tg_cp_async_arrive(xfull_bar(my_x));                         // 32 arrivals complete the slot
 #pragma unroll
             for (int j = 0; j < 16; ++j) cur[j] = nxt[j];
-            xcur[0] = xnxt[0]; xcur[1] = xnxt[1];
         }
     } else {
         // ------------------------------------------------------------ expanders: packed bytes -> fp16 weights in TMEM
@@ -430,7 +471,6 @@ __global__ void __launch_bounds__(TG_THREADS, 1) gemv4_tc_kernel(const __grid_co
         const int row = 32 * r + lane;
         const uint32_t woff0 = (uint32_t)(row * 128 + (((2 * b) ^ (row & 7)) << 4));
         const uint32_t woff1 = (uint32_t)(row * 128 + (((2 * b + 1) ^ (row & 7)) << 4));
-        const uint32_t aoff = (uint32_t)(TG_X_BYTES + (b * TG_ROWS + row) * 4);
         const uint32_t lane_word = TG_LUT_ABS | ((uint32_t)lane * 4u);   // bytes 0, 2, 3 of every table address
         const uint32_t tmem_mine = tmem_base + ((uint32_t)(32 * r) << 16) + (uint32_t)(32 * b);
         int slot = 0, xslot = 0, abuf = 0;
@@ -452,7 +492,15 @@ __global__ void __launch_bounds__(TG_THREADS, 1) gemv4_tc_kernel(const __grid_co
         };
         auto expand = [&](const uint4 &lo, const uint4 &hi) {
             if (!mbar_wait_sleep(xfull_bar(xslot), xph, abort_flag, kSleepFast)) { atomicExch(&g_tc_status, 408); *abort_flag = 1; ok = false; return; }
-            const float scale = tg_lds_f32(s_xs + (uint32_t)(xslot * TG_XS_BYTES) + aoff);
+            // my (row, block) scale: fp32 [row][4], or int8 codes [row] + second-level maximum [row]
+            const uint32_t ab = s_xs + (uint32_t)(xslot * TG_XS_BYTES) + TG_X_BYTES;
+            float scale;
+            if (tg_lds_u32(s_mode + 4u * xslot) != 0u) {
+                const int code = (int)(int8_t)((tg_lds_u32(ab + (uint32_t)(row * 4)) >> (8 * b)) & 0xFFu);
+                scale = (float)code * __fdiv_rn(tg_lds_f32(ab + 512u + (uint32_t)(row * 4)), 127.0f);
+            } else {
+                scale = tg_lds_f32(ab + (uint32_t)(row * 16 + b * 4));
+            }
             const uint32_t s2 = tg_pair_bits<XT>(scale, scale);
             const uint32_t wv[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
             uint32_t out[32];
@@ -547,7 +595,9 @@ static int tc_fill_linear(TcLinear &L, const TcHostLinear &h, int y_dtype) {
     L.x_period = (int)(h.x_period > 0 ? h.x_period : h.K);
     L.y_dtype = y_dtype;
     L.x_vec_ok = (h.x_ld % 8 == 0) && (L.x_period % 8 == 0) && (h.K % 8 == 0) && aligned16(h.x);
-    L.pad0 = L.pad1 = 0;
+    L.scale_async = (L.nb % 4 == 0) && ((reinterpret_cast<uintptr_t>(h.absmax) & 15) == 0) &&
+                    (h.absmax2 == nullptr || (reinterpret_cast<uintptr_t>(h.absmax2) & 3) == 0);
+    L.pad1 = 0;
     return MPSBNB_OK;
 }
 

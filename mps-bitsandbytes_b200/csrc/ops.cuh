@@ -33,5 +33,6 @@ int tc_run(const mpsbnb_group_plan *plan, cudaStream_t st);
 int tc_status_fetch(int *out, bool reset);
 // true when the environment selects the tcgen05 decode kernel (MPSBNB_GEMV_IMPL=tc)
 bool decode_uses_tensor_path();
+int decode_kernel_select(int which);
 
 }  // namespace mpsbnb
