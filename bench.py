@@ -1,7 +1,7 @@
 """Benchmark of the fused dequantise-matmul hot path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--batch M]
-                    [--layers L] [--skip-extras]
+                    [--layers L] [--skip-extras] [--prefill-only]
 
 Workload (N = 1): the Llama-2-7B-shaped NF4 decode stack of BASELINE config 3 — 32 layers x
 {q,k,v,o 4096x4096, gate/up 11008x4096, down 4096x11008}, double-quantised absmax, fp16,
@@ -20,6 +20,9 @@ line names it) and --skip-extras leaves out the prefill object and the CPU basel
 region is bracketed by cudaProfilerStart/Stop so that a profiler started with
 --profile-from-start off sees exactly the timed launches.
 
+--prefill-only runs just the prefill GEMM of BASELINE config 2 and prints its object (used for
+profiler captures of the tcgen05 GEMM).
+
 --impl reference times the reference's CPU algorithm (the C oracle: dequantise the whole
 weight, then matmul, as mps_bitsandbytes/functional.py:752-773 does on CPU) on one layer of
 the same stack per step, on all host cores.
@@ -35,6 +38,11 @@ import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
+
+
+# dram__bytes_read.sum + dram__bytes_write.sum of ONE gemv4_stream_kernel launch (one Llama-2-7B layer, batch 1,
+# whole layer on one GPU), from the ncu capture summarised in profiles/gemv4_stream_kernel_llama7b_layer.md
+NCU_TRAFFIC_7B_LAYER_BYTES = 108.5e6
 
 
 def load_peaks():
@@ -122,10 +130,20 @@ def cpu_baseline(cfg, M, budget_s=12.0):
         cpu_layer_pass(layer)
         best = min(best, time.perf_counter() - t0)
         reps += 1
-    nbytes = S.algorithmic_bytes(cfg, M, double_quant=False, layers=1)
+    nbytes = S.algorithmic_bytes(cfg, M, layers=1)           # same byte count per layer as the GPU arm
     return {"value": nbytes / best / 1e9, "unit": "GB/s", "cores": os.cpu_count(), "kind": "port",
-            "sample": f"1 of {cfg.layers} layers ({nbytes / 1e6:.0f} MB, 7 linears, random codes), best of {reps}, "
-                      f"C oracle of functional.py:752-773 with OpenMP"}
+            "sample": f"1 of {cfg.layers} layers ({nbytes / 1e6:.0f} MB, 7 linears, random codes, absmax already expanded to "
+                      f"fp32), best of {reps}, C oracle of functional.py:752-773 with OpenMP"}
+
+
+def workload_config(cfg, M, layers, world):
+    """The `config` object: the same in both arms."""
+    from mps_bitsandbytes_b200 import stack as S
+    nbytes = S.algorithmic_bytes(cfg, M, layers=layers)
+    return {"workload": f"{cfg.name} NF4+DQ decode stack ({layers} layers x 7 Linear4bit), batch {M}, "
+                        f"N-sharded over {world} GPU(s)", "batch": M, "layers": layers,
+            "l2": f"inputs ({nbytes / 1e9:.2f} GB of weights per step) larger than L2; no flush needed",
+            "parallelism": f"n-shard{world}"}
 
 
 def run_reference(args, cfg):
@@ -140,14 +158,14 @@ def run_reference(args, cfg):
     for _ in range(args.steps):
         cpu_layer_pass(layer)
     dt = (time.perf_counter() - t0) / args.steps
-    nbytes = S.algorithmic_bytes(cfg, args.batch, double_quant=False, layers=1)
+    nbytes = S.algorithmic_bytes(cfg, args.batch, layers=1)  # same byte count per layer as the GPU arm
     gbs = nbytes / dt / 1e9
     sample = f"each step = 1 of {cfg.layers} layers ({nbytes / 1e6:.0f} MB), C oracle of the reference CPU path, OpenMP"
     print(json.dumps({
         "impl": "reference", "metric": "nf4_decode_gbs", "value": gbs, "unit": "GB/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-        "config": {"workload": f"{cfg.name} NF4 decode stack, batch {args.batch}", "batch": args.batch},
+        "config": workload_config(cfg, args.batch, args.layers or cfg.layers, args.gpus),
         "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": os.cpu_count(), "kind": "port", "sample": sample},
         "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0}))
@@ -257,12 +275,11 @@ def run_gpu(args, cfg):
             "metric": "nf4_decode_gbs", "value": gbs, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-            "config": {"workload": f"{cfg.name} NF4+DQ decode stack ({stack.layers} layers x 7 Linear4bit), batch {M}, "
-                                   f"N-sharded over {world} GPU(s)", "batch": M, "layers": stack.layers,
-                       "l2": f"inputs ({nbytes / 1e9:.2f} GB of weights per step) larger than L2; no flush needed",
-                       "parallelism": f"n-shard{world}", "outputs_finite": finite},
+            "config": dict(workload_config(cfg, M, stack.layers, world), outputs_finite=finite),
             "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                         "frac": per_gpu / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"],
+                         "frac": per_gpu / peaks["hbm_gbs"],
+                         "traffic": NCU_TRAFFIC_7B_LAYER_BYTES if (grouped and world == 1 and M == 1 and cfg.name == "llama2-7b") else None,
+                         "peak_source": peaks["source"],
                          "kernel": kname, "launches_per_step": n_gemv,
                          "bytes_per_launch": nbytes / world / n_gemv,
                          "note": "achieved = algorithmic bytes of the step / CUDA-event time of the whole step "
@@ -298,10 +315,14 @@ def main():
     ap.add_argument("--model", default="llama2-7b", choices=["llama2-7b", "llama-70b"])
     ap.add_argument("--layers", type=int, default=None, help="reduced depth, for profiler captures")
     ap.add_argument("--skip-extras", action="store_true", help="no prefill object, no CPU baseline")
+    ap.add_argument("--prefill-only", action="store_true", help="only the prefill GEMM object (BASELINE config 2)")
     args = ap.parse_args()
     from mps_bitsandbytes_b200 import stack as S
     cfg = S.LLAMA2_7B if args.model == "llama2-7b" else S.LLAMA_70B
-    if args.impl == "reference":
+    if args.prefill_only:
+        import torch
+        print(json.dumps(prefill_config2(torch, load_peaks(), steps=args.steps, warmup=max(args.warmup, 3))))
+    elif args.impl == "reference":
         run_reference(args, cfg)
     else:
         run_gpu(args, cfg)
