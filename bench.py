@@ -291,6 +291,7 @@ def run_gpu(args, cfg):
         }
     if world > 1:
         dist.barrier()
+        torch.cuda.synchronize()
     if rank == 0:
         if world == 1 and not args.skip_extras:
             del stack
@@ -300,9 +301,12 @@ def run_gpu(args, cfg):
             except Exception as ex:                                  # reported, never hidden
                 out["prefill"] = {"error": repr(ex)}
             out["cpu_baseline"] = cpu_baseline(cfg, M)
-        print(json.dumps(out))
+        print(json.dumps(out), flush=True)
     if world > 1:
-        dist.destroy_process_group()
+        # The captured step holds NCCL kernels; tearing the communicator down under a live graph can block.
+        # Every rank is past the last collective (barrier above), so leave without the teardown.
+        sys.stdout.flush(); sys.stderr.flush()
+        os._exit(0)
 
 
 def main():
