@@ -246,12 +246,12 @@ def run_gpu(args, cfg):
     ms = e0.elapsed_time(e1) / args.steps
     # ---- end to end: pinned host input -> device, all layers, result back to host, every step
     for _ in range(3):
-        stack.step(x_host); y_host.copy_(stack.h, non_blocking=True); torch.cuda.synchronize()
+        stack.step(x_host); y_host.copy_(stack.output(), non_blocking=True); torch.cuda.synchronize()
     barrier()
     t0 = time.perf_counter()
     for _ in range(args.steps):
         stack.step(x_host)
-        y_host.copy_(stack.h, non_blocking=True)
+        y_host.copy_(stack.output(), non_blocking=True)
         torch.cuda.synchronize()
     barrier()
     e2e_ms = (time.perf_counter() - t0) * 1e3 / args.steps
@@ -260,7 +260,7 @@ def run_gpu(args, cfg):
         t = torch.tensor([ms, e2e_ms], device="cuda", dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms, e2e_ms = float(t[0]), float(t[1])
-    finite = bool(torch.isfinite(stack.h.float()).all())
+    finite = bool(torch.isfinite(stack.output().float()).all())
 
     nbytes = S.algorithmic_bytes(cfg, M, layers=stack.layers)    # whole model, all ranks together
     gbs = nbytes / (ms * 1e-3) / 1e9

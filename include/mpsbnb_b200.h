@@ -136,6 +136,22 @@ typedef struct mpsbnb_linear4_desc {
  * variable MPSBNB_GEMV_IMPL=tc sets the initial value to 1.  No reference counterpart. */
 int mpsbnb_decode_kernel_select(int which);
 
+/* Optional closing step of a grouped launch, run inside the kernel by the CTA that finishes last (so no
+ * separate boundary kernel is needed): h_shard = alpha * acc (acc: fp32 [M, hs], re-armed to zero) is
+ * stored into columns [rank * hs, (rank + 1) * hs) of every peer_h[r] ([M, H] in the activation dtype,
+ * r < nranks; a device array of pointers, own buffer included; nranks = 1, hs = H on a single GPU), and
+ * then, if peer_flags is not NULL, peer_flags[r][rank] = (*step) * mul + add for every r.
+ * counter: a device int that is zero between launches.  acc == NULL: no closing step. */
+typedef struct mpsbnb_group_epilogue {
+    float *acc;
+    void *const *peer_h;
+    int *const *peer_flags;
+    const int *step;
+    int *counter;
+    float alpha;
+    int M, hs, H, rank, nranks, mul, add;
+} mpsbnb_group_epilogue;
+
 typedef struct mpsbnb_group_plan {
     void *dev;
     int64_t units_offset;
@@ -143,6 +159,13 @@ typedef struct mpsbnb_group_plan {
     int flags;               /* set by the caller before a run: MPSBNB_GROUP_PDL or 0 */
     int64_t aux_offset;      /* filled by the plan call: per-CTA table inside the plan memory */
     int grid, impl;          /* filled by the plan call: CTAs to launch, kernel family */
+    /* Optional, set by the caller before a run (zero = off): before its first read of x the kernel waits,
+     * for at most about a second, until each of the wait_n ints at wait_flags (memory of this GPU) is
+     * >= (*wait_step) * wait_mul + wait_add.  Used with mpsbnb_stack_boundary_push on the other GPUs. */
+    const int *wait_flags;
+    const int *wait_step;
+    int wait_n, wait_mul, wait_add, pad_;
+    mpsbnb_group_epilogue ep; /* optional, set by the caller before a run (default kernel only) */
 } mpsbnb_group_plan;
 
 /* Launch with programmatic dependent launch: the kernel may start (build its tables, fetch
@@ -169,6 +192,31 @@ int mpsbnb_stack_boundary(const void *o, const void *d, int dtype, float alpha, 
  * No reference counterpart. */
 int mpsbnb_stack_boundary_acc(float *acc, float alpha, int64_t n, void *h, int dtype, int flags,
                               void *stream);   /* flags: MPSBNB_GROUP_PDL or 0 */
+
+/* Layer-boundary exchange of the N-sharded stack without a collective call (one process per GPU).
+ * No reference counterpart (the reference is single-device).
+ *  - mpsbnb_ipc_export / _open / _close: CUDA IPC plumbing for a buffer the CALLER allocated: export
+ *    gives the 64-byte handle of the allocation containing dev_ptr and dev_ptr's offset in it; a peer
+ *    process opens the handle (base address in its own address space, peer access enabled) and closes
+ *    it when done.  A process cannot open its own handle.
+ *  - mpsbnb_stack_boundary_push: h_shard = alpha * acc (acc: fp32 [M, hs], re-armed to zero) is stored
+ *    into columns [rank * hs, (rank + 1) * hs) of peer_h[r] ([M, H], r = 0 .. nranks-1, own buffer
+ *    included; device array of pointers) and then peer_flags[r][rank] = (*step) * mul + add for every r
+ *    (device array of pointers to each rank's int[nranks] flag array).  One small kernel; hs % 8 == 0.
+ *  - mpsbnb_flags_wait: a kernel that waits (bounded, status 502 on time-out) until flags[0..n) >=
+ *    (*step) * mul + add: put it at the end of a step so that the host reads a complete h.
+ *  - mpsbnb_flags_push: peer_flags[r][rank] = (*step) * mul + add for every r, without data (the
+ *    end-of-step acknowledgement: "my h buffers may be overwritten again").
+ *  - mpsbnb_counter_add: *counter += value on the stream (the step counter, inside a CUDA graph). */
+int mpsbnb_ipc_export(const void *dev_ptr, void *handle64, int64_t *offset_out);
+int mpsbnb_ipc_open(const void *handle64, void **base_out);
+int mpsbnb_ipc_close(void *base);
+int mpsbnb_stack_boundary_push(float *acc, float alpha, int64_t M, int64_t hs, int64_t H, int rank, int nranks,
+                               void *const *peer_h, int *const *peer_flags, const int *step, int mul, int add,
+                               int dtype, int flags, void *stream);
+int mpsbnb_flags_wait(const int *flags, int n, const int *step, int mul, int add, int pdl, void *stream);
+int mpsbnb_flags_push(int *const *peer_flags, int rank, int nranks, const int *step, int mul, int add, void *stream);
+int mpsbnb_counter_add(int *counter, int value, void *stream);
 
 /* Multi-GPU form of the boundary: G[r][m][c] holds the all-gathered per-rank shards of the
  * new h (c < H / nranks); writes h[m, r*H/nranks + c] = G[r][m][c] and e as above.

@@ -309,6 +309,9 @@ extern "C" int mpsbnb_device_status(int *status_out, int reset) {
     const int rc2 = tc_status_fetch(&other, reset != 0);
     if (rc2 != MPSBNB_OK) return rc2;
     if (*status_out == 0) *status_out = other;
+    const int rc3 = xchg_status_fetch(&other, reset != 0);
+    if (rc3 != MPSBNB_OK) return rc3;
+    if (*status_out == 0) *status_out = other;
     return MPSBNB_OK;
 }
 

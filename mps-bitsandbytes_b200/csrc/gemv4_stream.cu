@@ -86,6 +86,10 @@ struct StreamArgs {
     const StreamUnit *units;  // device array, or nullptr: unit u = rows [32 u, 32 u + 32) x all stages of `one`
     int nunits, M, quant_type;
     uint32_t zero;            // always 0; known only at run time (orders the slot release after the loads)
+    const int *wait_flags;    // wait_n flags in this GPU's memory that the loaders wait for before the first read of x:
+    const int *wait_step;     //   every flag >= (*wait_step) * wait_mul + wait_add  (peers raise them, see exchange.cu)
+    int wait_n, wait_mul, wait_add;
+    mpsbnb_group_epilogue ep; // closing step by the last CTA (ep.acc == nullptr: none)
     uint32_t sleep_cons;      // ns a consumer warp sleeps between probes of a barrier that is not ready
     uint32_t sleep_other;     // same for the producer, loader and reducer warps
     StreamLinear one;
@@ -467,12 +471,31 @@ __global__ void __launch_bounds__(SG_THREADS, 1) gemv4_stream_kernel(const __gri
             __syncwarp();
             if (lane == 0) mbar_arrive(red_empty(buf));
         }
+        __threadfence();                                         // my results before this CTA's arrival at the closing step
     } else if (warp > SG_CONSUMERS) {
         // ------------------------------------------------------------ loaders: block scales and x into the scale/x ring
         // SG_LOADERS warps take stages in turn; each reads the scales of its NEXT stage before it stores
         // the current one, so two rounds of global loads are in flight per warp.
         const int me = warp - SG_CONSUMERS - 1;
         pdl_grid_dependency_wait();                              // x is written by the previous kernel in the stream
+        if (a.wait_n > 0) {
+            // ... and, in the N-sharded stack, by the boundary kernels of the other GPUs: wait (bounded) for their flags
+            const int expect = (*a.wait_step) * a.wait_mul + a.wait_add;
+            bool arrived = true;
+            if (lane < a.wait_n) {
+                const long long t0 = clock64();
+                for (;;) {
+                    int v;
+                    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(a.wait_flags + lane) : "memory");
+                    if (v >= expect) break;
+                    __nanosleep(64);
+                    if (*abort_flag != 0 || clock64() - t0 > 2000000000ll) { arrived = false; break; }
+                }
+            }
+            arrived = __all_sync(0xffffffffu, arrived);
+            asm volatile("fence.proxy.async;" ::: "memory");      // x is then read by bulk copies (async proxy)
+            if (!arrived) { atomicExch(&g_stream_status, 207); *abort_flag = 1; }
+        }
         {
             auto read_scales = [&](const StreamLinear *L, int row0, int s, float (&sc)[16]) {
                 const int n = row0 + lane;
@@ -748,10 +771,44 @@ __global__ void __launch_bounds__(SG_THREADS, 1) gemv4_stream_kernel(const __gri
     }
     // After a time-out the roles leave early while copies may still be on their way into this CTA's
     // shared memory: give them a bounded moment to land before the CTA retires.
+    __syncthreads();                                                 // every role of this CTA is done
     if (*abort_flag) {
         const long long t0 = clock64();
         while (clock64() - t0 < 400000ll) { }
+        return;
     }
+    if (a.ep.acc == nullptr) return;
+    // ---- closing step: the CTA that finishes last turns the accumulated o + down into the next layer's input
+    volatile uint32_t *last_flag = abort_flag + 1;
+    if (tid == 0) {
+        __threadfence();
+        *last_flag = atomicAdd(a.ep.counter, 1) == (int)gridDim.x - 1 ? 1u : 0u;
+    }
+    __syncthreads();
+    if (*last_flag == 0u) return;
+    __threadfence();
+    {
+        const int total = a.ep.M * a.ep.hs;                          // hs is a multiple of 8
+        XT *const *peers = reinterpret_cast<XT *const *>(a.ep.peer_h);
+        for (int i = tid * 8; i < total; i += SG_THREADS * 8) {
+            const int m = i / a.ep.hs, c = i - m * a.ep.hs;
+            const float4 a0 = __ldcg(reinterpret_cast<const float4 *>(a.ep.acc + i));
+            const float4 a1 = __ldcg(reinterpret_cast<const float4 *>(a.ep.acc + i + 4));
+            *reinterpret_cast<float4 *>(a.ep.acc + i) = make_float4(0.f, 0.f, 0.f, 0.f);
+            *reinterpret_cast<float4 *>(a.ep.acc + i + 4) = make_float4(0.f, 0.f, 0.f, 0.f);
+            const float al = a.ep.alpha;
+            XT v[8] = {from_f32<XT>(al * a0.x), from_f32<XT>(al * a0.y), from_f32<XT>(al * a0.z), from_f32<XT>(al * a0.w),
+                       from_f32<XT>(al * a1.x), from_f32<XT>(al * a1.y), from_f32<XT>(al * a1.z), from_f32<XT>(al * a1.w)};
+            const uint4 bits = *reinterpret_cast<const uint4 *>(v);
+            const int64_t o = (int64_t)m * a.ep.H + (int64_t)a.ep.rank * a.ep.hs + c;
+            for (int r = 0; r < a.ep.nranks; ++r) *reinterpret_cast<uint4 *>(peers[r] + o) = bits;
+        }
+    }
+    __threadfence_system();                                          // the stores before the flags
+    __syncthreads();
+    if (tid == 0) *a.ep.counter = 0;
+    if (a.ep.peer_flags != nullptr && tid < a.ep.nranks)
+        asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(a.ep.peer_flags[tid] + a.ep.rank), "r"((*a.ep.step) * a.ep.mul + a.ep.add) : "memory");
 }
 
 // ------------------------------------------------------------------------------------------
@@ -875,6 +932,7 @@ int gemv4_stream_single(const void *x, int x_dtype, int64_t M, const uint8_t *pa
                         const float *absmax2, int64_t N, int64_t K, int quant_type, const void *bias, void *y,
                         int y_dtype, cudaStream_t st) {
     StreamArgs args;
+    memset(&args, 0, sizeof(args));
     args.lins = nullptr; args.units = nullptr;
     HostLinear h{x, K, K, packed, absmax, absmax2, bias, y, nullptr, N, K};
     int rc = fill_linear(args.one, h, y_dtype);
@@ -976,17 +1034,35 @@ extern "C" int mpsbnb_gemv_4bit_group_plan(const mpsbnb_linear4_desc *descs, int
     plan_out->aux_offset = 0;
     plan_out->grid = 0;
     plan_out->impl = 0;
+    plan_out->wait_flags = nullptr; plan_out->wait_step = nullptr;
+    plan_out->wait_n = plan_out->wait_mul = plan_out->wait_add = plan_out->pad_ = 0;
+    memset(&plan_out->ep, 0, sizeof(plan_out->ep));
     return MPSBNB_OK;
 }
 
 extern "C" int mpsbnb_gemv_4bit_group_run(const mpsbnb_group_plan *plan, void *stream) {
     if (plan == nullptr || plan->dev == nullptr || plan->n_units <= 0) return MPSBNB_ERR_INVALID_ARG;
-    if (plan->impl == 1) return plan->grid > 0 ? tc_run(plan, (cudaStream_t)stream) : MPSBNB_ERR_INVALID_ARG;
+    if (plan->impl == 1) {
+        if (plan->wait_n > 0 || plan->ep.acc != nullptr) return MPSBNB_ERR_UNSUPPORTED;   // both live in the default kernel
+        return plan->grid > 0 ? tc_run(plan, (cudaStream_t)stream) : MPSBNB_ERR_INVALID_ARG;
+    }
     StreamArgs args;
     memset(&args, 0, sizeof(args));
     args.lins = reinterpret_cast<const StreamLinear *>(plan->dev);
     args.units = reinterpret_cast<const StreamUnit *>(reinterpret_cast<const unsigned char *>(plan->dev) + plan->units_offset);
     args.nunits = plan->n_units; args.M = plan->M; args.quant_type = plan->quant_type;
+    if (plan->wait_n > 0) {
+        if (plan->wait_flags == nullptr || plan->wait_step == nullptr || plan->wait_n > 32) return MPSBNB_ERR_INVALID_ARG;
+        args.wait_flags = plan->wait_flags; args.wait_step = plan->wait_step;
+        args.wait_n = plan->wait_n; args.wait_mul = plan->wait_mul; args.wait_add = plan->wait_add;
+    }
+    if (plan->ep.acc != nullptr) {
+        const mpsbnb_group_epilogue &e = plan->ep;
+        if (e.peer_h == nullptr || e.counter == nullptr || e.M != plan->M || e.hs <= 0 || e.hs % 8 != 0 || e.nranks <= 0 ||
+            e.nranks > 32 || e.rank < 0 || e.rank >= e.nranks || e.H < e.hs * e.nranks || (e.peer_flags != nullptr && e.step == nullptr))
+            return MPSBNB_ERR_INVALID_ARG;
+        args.ep = e;
+    }
     const bool pdl = (plan->flags & MPSBNB_GROUP_PDL) != 0;
     return plan->x_dtype == MPSBNB_F16 ? launch_stream<__half>(args, (cudaStream_t)stream, pdl)
                                        : launch_stream<__nv_bfloat16>(args, (cudaStream_t)stream, pdl);

@@ -31,6 +31,7 @@ int tc_plan(const mpsbnb_linear4_desc *descs, int n_linears, int64_t M, int x_dt
             void *plan_dev, size_t plan_bytes, mpsbnb_group_plan *plan_out, cudaStream_t st);
 int tc_run(const mpsbnb_group_plan *plan, cudaStream_t st);
 int tc_status_fetch(int *out, bool reset);
+int xchg_status_fetch(int *out, bool reset);   // exchange.cu
 // true when the environment selects the tcgen05 decode kernel (MPSBNB_GEMV_IMPL=tc)
 bool decode_uses_tensor_path();
 int decode_kernel_select(int which);

@@ -95,12 +95,18 @@ class LayerStack:
 
     def __init__(self, cfg: StackConfig, device, quant_type: str = "nf4", double_quant: bool = True,
                  layers: Optional[int] = None, rank: int = 0, world: int = 1, seed: int = 1000,
-                 dtype: torch.dtype = torch.float16, group=None, use_pdl: bool = True):
+                 dtype: torch.dtype = torch.float16, group=None, use_pdl: bool = True, fused_exchange: bool = False, in_kernel_boundary: bool = False):
         self.cfg, self.device, self.dtype = cfg, torch.device(device), dtype
         self.layers = cfg.layers if layers is None else layers
         self.rank, self.world, self.group = rank, world, group
         # programmatic dependent launch between the per-layer kernels (single GPU: no NCCL kernel in between)
         self.use_pdl = use_pdl and world == 1
+        # world > 1, batch <= 8: the layer boundary stores its shard of h into every rank's buffer over NVLink and
+        # raises flags (csrc/exchange.cu) instead of calling an NCCL all-gather; decided in prepare()
+        self.fused_exchange = fused_exchange and world > 1
+        self.in_kernel_boundary = in_kernel_boundary
+        self._fused = False
+        self._peer_bases = []
         self.quant_type, self.double_quant = quant_type, double_quant
         self.alpha = cfg.alpha()
         if cfg.hidden % world or cfg.ffn % world or cfg.kv % world:
@@ -141,8 +147,58 @@ class LayerStack:
         self.acc = torch.zeros(M, cfg.hidden // g, dtype=torch.float32, device=dev)
         self._M = M
         self._plans = None
+        self._fused = self.fused_exchange and M <= 8
+        if self._fused:
+            self._setup_exchange(M)
         if M <= 8:
             self._build_plans(M)
+
+    # ------------------------------------------------------------------ fused exchange (world > 1, batch <= 8)
+    def _setup_exchange(self, M: int):
+        """One exported buffer per rank: h double-buffered by layer parity [2, M, H], flags int32[g] (raised by the
+        boundary kernels of all ranks), acks int32[g] (raised at the end of a step).  Peers map it with CUDA IPC."""
+        cfg, dev, g, lib = self.cfg, self.device, self.world, N.lib()
+        self._close_exchange()
+        esz = torch.empty(0, dtype=self.dtype).element_size()
+        h_bytes = (2 * M * cfg.hidden * esz + 255) // 256 * 256
+        self._xbuf = torch.zeros(h_bytes + 512, dtype=torch.uint8, device=dev)
+        self.hbuf = self._xbuf[:2 * M * cfg.hidden * esz].view(self.dtype).view(2, M, cfg.hidden)
+        self.flags = self._xbuf[h_bytes:h_bytes + 4 * g].view(torch.int32)
+        self.acks = self._xbuf[h_bytes + 256:h_bytes + 256 + 4 * g].view(torch.int32)
+        self.step_ctr = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.h_out = torch.zeros(M, cfg.hidden, dtype=self.dtype, device=dev)
+        handle = (C.c_ubyte * 64)()
+        off = C.c_int64(0)
+        N.check(lib.mpsbnb_ipc_export(N.ptr(self._xbuf), handle, C.byref(off)), "ipc_export")
+        mine = (bytes(handle), int(off.value))
+        everyone = [None] * g
+        torch.cuda.synchronize()
+        torch.distributed.all_gather_object(everyone, mine, group=self.group)
+        bases = []
+        for r in range(g):
+            if r == self.rank:
+                bases.append(self._xbuf.data_ptr())
+                continue
+            hb = (C.c_ubyte * 64).from_buffer_copy(everyone[r][0])
+            base = C.c_void_p(0)
+            N.check(lib.mpsbnb_ipc_open(hb, C.byref(base)), "ipc_open")
+            self._peer_bases.append(base.value)
+            bases.append(base.value + everyone[r][1])
+        one = M * cfg.hidden * esz
+        self._peer_h = [torch.tensor([b + p * one for b in bases], dtype=torch.int64, device=dev) for p in (0, 1)]
+        self._peer_flags = torch.tensor([b + h_bytes for b in bases], dtype=torch.int64, device=dev)
+        self._peer_acks = torch.tensor([b + h_bytes + 256 for b in bases], dtype=torch.int64, device=dev)
+        torch.cuda.synchronize()
+        torch.distributed.barrier(group=self.group)              # every rank has mapped every buffer (all zero)
+
+    def _close_exchange(self):
+        for b in self._peer_bases:
+            N.lib().mpsbnb_ipc_close(C.c_void_p(b))
+        self._peer_bases = []
+
+    def _x_of_layer(self, l: int) -> torch.Tensor:
+        """Input h of layer l: the parity buffer in the fused exchange, else the one h."""
+        return self.hbuf[l & 1] if self._fused else self.h
 
     def _build_plans(self, M: int):
         """One grouped-launch plan per layer: q, k, v, gate, up store their outputs; o and down add
@@ -150,11 +206,13 @@ class LayerStack:
         its column index wrapped at H, which is the tiled input e without materialising it."""
         cfg, lib, g = self.cfg, N.lib(), self.world
         self._plans, self._plan_mem = [], []
+        self._ep_counter = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self._own_h = torch.tensor([self.h.data_ptr()], dtype=torch.int64, device=self.device)
         for l in range(self.layers):
             descs = (N.Linear4Desc * 7)()
             for i, pr in enumerate(self.proj[l]):
                 d = descs[i]
-                d.x, d.x_ld = self.h.data_ptr(), cfg.hidden
+                d.x, d.x_ld = self._x_of_layer(l).data_ptr(), cfg.hidden
                 d.x_period = cfg.hidden if pr.name == "down" else 0
                 d.packed, d.absmax = pr.packed.data_ptr(), pr.absmax.data_ptr()
                 d.absmax2 = None if pr.absmax2 is None else pr.absmax2.data_ptr()
@@ -170,7 +228,25 @@ class LayerStack:
             N.check(lib.mpsbnb_gemv_4bit_group_plan(descs, C.c_int(7), N.i64(M), N.dt(self.dtype), N.dt(self.dtype),
                                                     C.c_int(N.qt(self.quant_type)), N.ptr(mem), C.c_size_t(nbytes),
                                                     C.byref(plan), N.stream()), "gemv_4bit_group_plan")
-            plan.flags = N.GROUP_PDL if self.use_pdl else 0
+            plan.flags = N.GROUP_PDL if (self.use_pdl or self._fused) else 0
+            if self.in_kernel_boundary and (g == 1 or self._fused):
+                # the CTA that finishes last writes alpha * (o + down) as the next layer's h (into every rank's
+                # buffer when fused) and re-arms the accumulator: no boundary kernel
+                ep = plan.ep
+                ep.acc, ep.alpha, ep.counter = self.acc.data_ptr(), self.alpha, self._ep_counter.data_ptr()
+                ep.M, ep.hs, ep.H, ep.rank, ep.nranks = M, cfg.hidden // g, cfg.hidden, self.rank, g
+                if self._fused:
+                    ep.peer_h, ep.peer_flags = self._peer_h[(l + 1) & 1].data_ptr(), self._peer_flags.data_ptr()
+                    ep.step, ep.mul, ep.add = self.step_ctr.data_ptr(), self.layers, l + 1
+                else:
+                    ep.peer_h = self._own_h.data_ptr()
+            if self._fused:
+                # layer 0 waits for the acks of the previous step (every rank has copied its result out), the
+                # others for the boundary flags of the layer before
+                src = self.acks if l == 0 else self.flags
+                plan.wait_flags, plan.wait_step = src.data_ptr(), self.step_ctr.data_ptr()
+                plan.wait_n = g
+                plan.wait_mul, plan.wait_add = (1, 0) if l == 0 else (self.layers, l)
             self._plans.append(plan)
             self._plan_mem.append(mem)
 
@@ -190,10 +266,32 @@ class LayerStack:
     def _run_layers(self, M: int):
         """Enqueue one step (all layers) on the current stream."""
         cfg, lib, g = self.cfg, N.lib(), self.world
+        if self._plans is not None and self._fused:
+            hs, L = cfg.hidden // g, self.layers
+            for l in range(L):
+                N.check(lib.mpsbnb_gemv_4bit_group_run(C.byref(self._plans[l]), N.stream()), "gemv_4bit_group_run")
+                if self.in_kernel_boundary:
+                    continue
+                N.check(lib.mpsbnb_stack_boundary_push(N.ptr(self.acc), C.c_float(self.alpha), N.i64(M), N.i64(hs),
+                                                       N.i64(cfg.hidden), C.c_int(self.rank), C.c_int(g),
+                                                       N.ptr(self._peer_h[(l + 1) & 1]), N.ptr(self._peer_flags),
+                                                       N.ptr(self.step_ctr), C.c_int(L), C.c_int(l + 1), N.dt(self.dtype),
+                                                       C.c_int(N.GROUP_PDL), N.stream()), "stack_boundary_push")
+            # the step is complete here once every rank's last shard has landed; keep the result in a buffer no
+            # peer writes, then tell the peers (acks) that this rank's h buffers may be overwritten again
+            N.check(lib.mpsbnb_flags_wait(N.ptr(self.flags), C.c_int(g), N.ptr(self.step_ctr), C.c_int(L), C.c_int(L),
+                                          C.c_int(1), N.stream()), "flags_wait")
+            self.h_out.copy_(self.hbuf[L & 1])
+            N.check(lib.mpsbnb_counter_add(N.ptr(self.step_ctr), C.c_int(1), N.stream()), "counter_add")
+            N.check(lib.mpsbnb_flags_push(N.ptr(self._peer_acks), C.c_int(self.rank), C.c_int(g), N.ptr(self.step_ctr),
+                                          C.c_int(1), C.c_int(0), N.stream()), "flags_push")
+            return
         if self._plans is not None:
             hs = cfg.hidden // g
             for l in range(self.layers):
                 N.check(lib.mpsbnb_gemv_4bit_group_run(C.byref(self._plans[l]), N.stream()), "gemv_4bit_group_run")
+                if self.in_kernel_boundary and g == 1:
+                    continue
                 dst = self.h if g == 1 else self.h_shard
                 N.check(lib.mpsbnb_stack_boundary_acc(N.ptr(self.acc), C.c_float(self.alpha), N.i64(M * hs), N.ptr(dst),
                                                       N.dt(self.dtype), C.c_int(N.GROUP_PDL if self.use_pdl else 0),
@@ -251,7 +349,7 @@ class LayerStack:
         """h = x_in, e = tile(x_in): the stack's input stage (uses the expand kernel with one rank)."""
         cfg = self.cfg
         N.check(N.lib().mpsbnb_stack_expand(N.ptr(self.x_in), N.dt(self.dtype), N.i64(1), N.i64(self._M),
-                                            N.i64(cfg.hidden), N.i64(cfg.ffn), N.ptr(self.h), N.ptr(self.e),
+                                            N.i64(cfg.hidden), N.i64(cfg.ffn), N.ptr(self._x_of_layer(0)), N.ptr(self.e),
                                             N.stream()), "stack_expand")
 
     def step(self, x: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -266,10 +364,18 @@ class LayerStack:
             else:
                 self._load_input()
                 self._run_layers(self._M)
-        return self.h
+        return self.h_out if self._fused else self.h
+
+    def output(self) -> torch.Tensor:
+        """h after the last layer of the latest step."""
+        return self.h_out if self._fused else self.h
 
     def launches_per_step(self) -> int:
         """Kernels of this library launched per step (NCCL's own kernels not counted)."""
+        if self._plans is not None and self._fused:
+            return 1 + self.layers * (1 if self.in_kernel_boundary else 2) + 3                          # + flags_wait, counter_add, flags_push (the copy is torch's)
+        if self._plans is not None and self.world == 1 and self.in_kernel_boundary:
+            return 1 + self.layers
         if self._plans is not None:
             return 1 + self.layers * (2 if self.world == 1 else 3)
         return 1 + self.layers * (7 + (1 if self.world == 1 else 2))

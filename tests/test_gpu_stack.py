@@ -28,11 +28,12 @@ def oracle_stack(st: S.LayerStack, x: np.ndarray):
     return h, outs
 
 
-@pytest.mark.parametrize("M", [1, 3, 8, 16])
+@pytest.mark.parametrize("M,in_kernel", [(1, True), (1, False), (3, True), (8, True), (8, False), (16, True)])
 @pytest.mark.parametrize("qt,dq", [("nf4", True), ("fp4", False)])
-def test_small_stack_matches_oracle(M, qt, dq):
+def test_small_stack_matches_oracle(M, in_kernel, qt, dq):
+    """in_kernel: the layer boundary is the closing step of the grouped GEMV launch; otherwise its own kernel."""
     cfg = S.StackConfig("tiny", hidden=256, ffn=704, kv=64, layers=3)
-    st = S.LayerStack(cfg, device="cuda:0", quant_type=qt, double_quant=dq, seed=5)
+    st = S.LayerStack(cfg, device="cuda:0", quant_type=qt, double_quant=dq, seed=5, in_kernel_boundary=in_kernel)
     rng = np.random.default_rng(M)
     x = rng.standard_normal((M, cfg.hidden)).astype(np.float16)
     for use_graph in (False, True):

@@ -11,7 +11,7 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def _worker(rank, world, port, M):
+def _worker(rank, world, port, M, fused):
     import torch.distributed as dist
     from mps_bitsandbytes_b200 import stack as S
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
@@ -22,7 +22,7 @@ def _worker(rank, world, port, M):
     whole = S.LayerStack(cfg, device=f"cuda:{rank}", seed=21)                   # the same model on every rank
     whole.prepare(M, use_graph=False)
     ref = whole.step(x).float().clone()
-    part = S.LayerStack(cfg, device=f"cuda:{rank}", seed=21, rank=rank, world=world)
+    part = S.LayerStack(cfg, device=f"cuda:{rank}", seed=21, rank=rank, world=world, fused_exchange=fused)
     ok = True
     for use_graph in (False, True):
         part.prepare(M, use_graph=use_graph)
@@ -31,6 +31,10 @@ def _worker(rank, world, port, M):
             torch.cuda.synchronize()
             err = float((h - ref).abs().max() / ref.abs().max())
             ok = ok and err <= 2e-3
+    import ctypes as C
+    from mps_bitsandbytes_b200 import _native
+    code = C.c_int(0)
+    ok = ok and _native.lib().mpsbnb_device_status(C.byref(code), C.c_int(1)) == 0 and code.value == 0
     flag = torch.tensor([1 if ok else 0], device="cuda")
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     torch.cuda.synchronize()
@@ -39,15 +43,16 @@ def _worker(rank, world, port, M):
     os._exit(0 if int(flag.item()) == 1 else 1)
 
 
-@pytest.mark.parametrize("M", [1, 16])
-def test_two_rank_stack_matches_single_gpu(M):
+@pytest.mark.parametrize("M,fused", [(1, True), (4, True), (1, False), (16, True)])
+def test_two_rank_stack_matches_single_gpu(M, fused):
+    """fused: peer stores + flags at the layer boundary (batch <= 8); otherwise NCCL all-gather."""
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     import torch.multiprocessing as mp
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
         port = s.getsockname()[1]
-    ctx = mp.spawn(_worker, args=(2, port, M), nprocs=2, join=False)
+    ctx = mp.spawn(_worker, args=(2, port, M, fused), nprocs=2, join=False)
     # bounded: a rank that never joins must not hold the suite
     for p in ctx.processes:
         p.join(timeout=180)
