@@ -216,7 +216,7 @@ def run_gpu(args, cfg):
     peaks = load_peaks()
     M = args.batch
     stack = S.LayerStack(cfg, device=f"cuda:{local}", rank=rank, world=world, layers=args.layers,
-                         fused_exchange=args.exchange == "fused", in_kernel_boundary=args.boundary == "inline")
+                         fused_exchange=args.exchange == "fused", boundary=args.boundary)
     stack.prepare(M, use_graph=True)
     gen = torch.Generator(device="cpu"); gen.manual_seed(1)
     x_host = torch.randn(M, cfg.hidden, generator=gen).half().pin_memory()
@@ -323,8 +323,9 @@ def main():
     ap.add_argument("--prefill-only", action="store_true", help="only the prefill GEMM object (BASELINE config 2)")
     ap.add_argument("--exchange", default="fused", choices=["fused", "nccl"],
                     help="N > 1: layer boundary by peer stores + flags (default) or by an NCCL all-gather")
-    ap.add_argument("--boundary", default="kernel", choices=["kernel", "inline"],
-                    help="layer boundary as its own small kernel (default) or as the closing step of the GEMV launch")
+    ap.add_argument("--boundary", default=None, choices=["kernel", "inline", "stream"],
+                    help="layer boundary: its own small kernel (default on one GPU), the closing step of the GEMV "
+                         "launch, or streamed tile by tile from inside the launch (default with the fused exchange)")
     args = ap.parse_args()
     from mps_bitsandbytes_b200 import stack as S
     cfg = S.LLAMA2_7B if args.model == "llama2-7b" else S.LLAMA_70B

@@ -141,15 +141,23 @@ int mpsbnb_decode_kernel_select(int which);
  * stored into columns [rank * hs, (rank + 1) * hs) of every peer_h[r] ([M, H] in the activation dtype,
  * r < nranks; a device array of pointers, own buffer included; nranks = 1, hs = H on a single GPU), and
  * then, if peer_flags is not NULL, peer_flags[r][rank] = (*step) * mul + add for every r.
- * counter: a device int that is zero between launches.  acc == NULL: no closing step. */
+ * counter: a device int that is zero between launches.  acc == NULL: no closing step.
+ * tile_cnt != NULL selects the streamed form instead: every 32-row tile of acc is converted, stored and
+ * re-armed as soon as the last of its tile_expect contributions (plan.acc_parts: the units of all linears
+ * that add into acc) has arrived — tile_cnt: hs / 32 device ints, zero between launches — and the flags
+ * are raised after the last tile.  Linears with an accumulator are scheduled first in a launch, so this
+ * happens early and the exchange hides behind the rest of the launch.  Because h of the NEXT layer is
+ * then written while THIS layer is still reading its own h, peer_h must not be the buffer the launch reads
+ * x from (rotate three buffers when ranks may run more than a layer apart). */
 typedef struct mpsbnb_group_epilogue {
     float *acc;
     void *const *peer_h;
     int *const *peer_flags;
     const int *step;
     int *counter;
+    int *tile_cnt;
     float alpha;
-    int M, hs, H, rank, nranks, mul, add;
+    int M, hs, H, rank, nranks, mul, add, tile_expect;
 } mpsbnb_group_epilogue;
 
 typedef struct mpsbnb_group_plan {
@@ -164,7 +172,8 @@ typedef struct mpsbnb_group_plan {
      * >= (*wait_step) * wait_mul + wait_add.  Used with mpsbnb_stack_boundary_push on the other GPUs. */
     const int *wait_flags;
     const int *wait_step;
-    int wait_n, wait_mul, wait_add, pad_;
+    int wait_n, wait_mul, wait_add;
+    int acc_parts;            /* filled by the plan call: units per 32-row tile that add into an accumulator */
     mpsbnb_group_epilogue ep; /* optional, set by the caller before a run (default kernel only) */
 } mpsbnb_group_plan;
 

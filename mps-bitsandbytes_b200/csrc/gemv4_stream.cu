@@ -470,6 +470,42 @@ __global__ void __launch_bounds__(SG_THREADS, 1) gemv4_stream_kernel(const __gri
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(red_empty(buf));
+            if (a.ep.tile_cnt != nullptr && L->acc == a.ep.acc && L->acc != nullptr) {
+                // streamed closing step: count this unit's contribution to its 32-row tile; whoever brings the
+                // last one converts the tile, stores it into every rank's h and re-arms the accumulator
+                __threadfence();
+                __syncwarp();
+                const int tile = un.row0 / SG_ROWS;
+                int old = 0;
+                if (lane == 0) old = atomicAdd(a.ep.tile_cnt + tile, 1);
+                old = __shfl_sync(0xffffffffu, old, 0);
+                if (old == a.ep.tile_expect - 1) {
+                    __threadfence();
+                    XT *const *peers = reinterpret_cast<XT *const *>(a.ep.peer_h);
+                    if (n < a.ep.hs) {
+                        for (int m = 0; m < a.M; ++m) {
+                            float *pa = a.ep.acc + (int64_t)m * a.ep.hs + n;
+                            const XT hv = from_f32<XT>(a.ep.alpha * __ldcg(pa));
+                            *pa = 0.0f;
+                            const int64_t o = (int64_t)m * a.ep.H + (int64_t)a.ep.rank * a.ep.hs + n;
+                            for (int r = 0; r < a.ep.nranks; ++r) peers[r][o] = hv;
+                        }
+                    }
+                    if (lane == 0) a.ep.tile_cnt[tile] = 0;
+                    __threadfence_system();
+                    __syncwarp();
+                    int done = 0;
+                    if (lane == 0) done = atomicAdd(a.ep.counter, 1);
+                    done = __shfl_sync(0xffffffffu, done, 0);
+                    if (done == (a.ep.hs + SG_ROWS - 1) / SG_ROWS - 1) {
+                        // every tile of this rank's shard has been stored (each store was fenced before its count)
+                        __threadfence_system();
+                        if (lane == 0) *a.ep.counter = 0;
+                        if (a.ep.peer_flags != nullptr && lane < a.ep.nranks)
+                            asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(a.ep.peer_flags[lane] + a.ep.rank), "r"((*a.ep.step) * a.ep.mul + a.ep.add) : "memory");
+                    }
+                }
+            }
         }
         __threadfence();                                         // my results before this CTA's arrival at the closing step
     } else if (warp > SG_CONSUMERS) {
@@ -777,7 +813,7 @@ __global__ void __launch_bounds__(SG_THREADS, 1) gemv4_stream_kernel(const __gri
         while (clock64() - t0 < 400000ll) { }
         return;
     }
-    if (a.ep.acc == nullptr) return;
+    if (a.ep.acc == nullptr || a.ep.tile_cnt != nullptr) return;
     // ---- closing step: the CTA that finishes last turns the accumulated o + down into the next layer's input
     volatile uint32_t *last_flag = abort_flag + 1;
     if (tid == 0) {
@@ -993,16 +1029,23 @@ extern "C" int mpsbnb_gemv_4bit_group_plan(const mpsbnb_linear4_desc *descs, int
     StreamLinear *lins = reinterpret_cast<StreamLinear *>(host);
     StreamUnit *units = reinterpret_cast<StreamUnit *>(host + lin_bytes);
     int rc = MPSBNB_OK;
+    int acc_parts = 0;
     for (int i = 0; i < n_linears && rc == MPSBNB_OK; ++i) {
         HostLinear h{descs[i].x, descs[i].x_ld, descs[i].x_period, descs[i].packed, descs[i].absmax, descs[i].absmax2,
                      descs[i].bias, descs[i].y, descs[i].acc, descs[i].N, descs[i].K};
         rc = fill_linear(lins[i], h, y_dtype);
     }
     if (rc == MPSBNB_OK) {
-        // units, longest first so that the round-robin remainder consists of the short ones
+        // units: linears that add into an accumulator first (what depends on them can then be finished while
+        // the rest of the launch still runs), within each class longest first so that the round-robin
+        // remainder consists of the short ones
         int nu2 = 0;
+        for (int i = 0; i < n_linears; ++i)
+            if (lins[i].acc != nullptr) acc_parts += ((lins[i].nb + SG_STAGE_BLOCKS - 1) / SG_STAGE_BLOCKS + chunk - 1) / chunk;
+        for (int cls = 0; cls < 2; ++cls)
         for (int pass = chunk * 8; pass >= 1; --pass) {
             for (int i = 0; i < n_linears; ++i) {
+                if ((lins[i].acc != nullptr) != (cls == 0)) continue;
                 const int S = (lins[i].nb + SG_STAGE_BLOCKS - 1) / SG_STAGE_BLOCKS;
                 const int step = lins[i].acc != nullptr ? chunk : S;
                 for (int s0 = 0; s0 < S; s0 += step) {
@@ -1035,7 +1078,8 @@ extern "C" int mpsbnb_gemv_4bit_group_plan(const mpsbnb_linear4_desc *descs, int
     plan_out->grid = 0;
     plan_out->impl = 0;
     plan_out->wait_flags = nullptr; plan_out->wait_step = nullptr;
-    plan_out->wait_n = plan_out->wait_mul = plan_out->wait_add = plan_out->pad_ = 0;
+    plan_out->wait_n = plan_out->wait_mul = plan_out->wait_add = 0;
+    plan_out->acc_parts = acc_parts;
     memset(&plan_out->ep, 0, sizeof(plan_out->ep));
     return MPSBNB_OK;
 }
@@ -1059,7 +1103,8 @@ extern "C" int mpsbnb_gemv_4bit_group_run(const mpsbnb_group_plan *plan, void *s
     if (plan->ep.acc != nullptr) {
         const mpsbnb_group_epilogue &e = plan->ep;
         if (e.peer_h == nullptr || e.counter == nullptr || e.M != plan->M || e.hs <= 0 || e.hs % 8 != 0 || e.nranks <= 0 ||
-            e.nranks > 32 || e.rank < 0 || e.rank >= e.nranks || e.H < e.hs * e.nranks || (e.peer_flags != nullptr && e.step == nullptr))
+            e.nranks > 32 || e.rank < 0 || e.rank >= e.nranks || e.H < e.hs * e.nranks || (e.peer_flags != nullptr && e.step == nullptr) ||
+            (e.tile_cnt != nullptr && (e.tile_expect <= 0 || e.tile_expect != plan->acc_parts)))
             return MPSBNB_ERR_INVALID_ARG;
         args.ep = e;
     }

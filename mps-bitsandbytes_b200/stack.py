@@ -95,7 +95,7 @@ class LayerStack:
 
     def __init__(self, cfg: StackConfig, device, quant_type: str = "nf4", double_quant: bool = True,
                  layers: Optional[int] = None, rank: int = 0, world: int = 1, seed: int = 1000,
-                 dtype: torch.dtype = torch.float16, group=None, use_pdl: bool = True, fused_exchange: bool = True, in_kernel_boundary: bool = False):
+                 dtype: torch.dtype = torch.float16, group=None, use_pdl: bool = True, fused_exchange: bool = True, boundary: Optional[str] = None):
         self.cfg, self.device, self.dtype = cfg, torch.device(device), dtype
         self.layers = cfg.layers if layers is None else layers
         self.rank, self.world, self.group = rank, world, group
@@ -104,7 +104,17 @@ class LayerStack:
         # world > 1, batch <= 8: the layer boundary stores its shard of h into every rank's buffer over NVLink and
         # raises flags (csrc/exchange.cu) instead of calling an NCCL all-gather; decided in prepare()
         self.fused_exchange = fused_exchange and world > 1
-        self.in_kernel_boundary = in_kernel_boundary
+        # layer boundary (h' = alpha (o + down)) of the grouped path: "kernel" = its own small kernel after the GEMV
+        # launch; "inline" = closing step of the GEMV launch (last CTA); "stream" = tile by tile inside the GEMV
+        # launch as soon as a tile's o and down contributions are complete (h rotates over three buffers)
+        # Measured: on one GPU the separate kernel is fastest (1.23 ms per 7B step vs 1.31 inline, 1.40 stream);
+        # across GPUs streaming hides the exchange (2 GPUs, 70B layers: 0.587 vs 0.631 ms)
+        if boundary is None:
+            boundary = "stream" if (world > 1 and fused_exchange) else "kernel"
+        if boundary not in ("kernel", "inline", "stream"):
+            raise ValueError("boundary must be 'kernel', 'inline' or 'stream'")
+        self.boundary = boundary
+        self.in_kernel_boundary = boundary != "kernel"
         self._fused = False
         self._peer_bases = []
         self.quant_type, self.double_quant = quant_type, double_quant
@@ -148,8 +158,12 @@ class LayerStack:
         self._M = M
         self._plans = None
         self._fused = self.fused_exchange and M <= 8
+        self._stream = self.boundary == "stream" and M <= 8 and (g == 1 or self._fused)
+        self._nbuf = 3 if self._stream else 2
         if self._fused:
             self._setup_exchange(M)
+        elif self._stream:
+            self.hbuf = torch.zeros(self._nbuf, M, cfg.hidden, dtype=dt, device=dev)
         if M <= 8:
             self._build_plans(M)
 
@@ -160,9 +174,10 @@ class LayerStack:
         cfg, dev, g, lib = self.cfg, self.device, self.world, N.lib()
         self._close_exchange()
         esz = torch.empty(0, dtype=self.dtype).element_size()
-        h_bytes = (2 * M * cfg.hidden * esz + 255) // 256 * 256
+        nb = self._nbuf
+        h_bytes = (nb * M * cfg.hidden * esz + 255) // 256 * 256
         self._xbuf = torch.zeros(h_bytes + 512, dtype=torch.uint8, device=dev)
-        self.hbuf = self._xbuf[:2 * M * cfg.hidden * esz].view(self.dtype).view(2, M, cfg.hidden)
+        self.hbuf = self._xbuf[:nb * M * cfg.hidden * esz].view(self.dtype).view(nb, M, cfg.hidden)
         self.flags = self._xbuf[h_bytes:h_bytes + 4 * g].view(torch.int32)
         self.acks = self._xbuf[h_bytes + 256:h_bytes + 256 + 4 * g].view(torch.int32)
         self.step_ctr = torch.zeros(1, dtype=torch.int32, device=dev)
@@ -185,7 +200,7 @@ class LayerStack:
             self._peer_bases.append(base.value)
             bases.append(base.value + everyone[r][1])
         one = M * cfg.hidden * esz
-        self._peer_h = [torch.tensor([b + p * one for b in bases], dtype=torch.int64, device=dev) for p in (0, 1)]
+        self._peer_h = [torch.tensor([b + p * one for b in bases], dtype=torch.int64, device=dev) for p in range(nb)]
         self._peer_flags = torch.tensor([b + h_bytes for b in bases], dtype=torch.int64, device=dev)
         self._peer_acks = torch.tensor([b + h_bytes + 256 for b in bases], dtype=torch.int64, device=dev)
         torch.cuda.synchronize()
@@ -198,7 +213,7 @@ class LayerStack:
 
     def _x_of_layer(self, l: int) -> torch.Tensor:
         """Input h of layer l: the parity buffer in the fused exchange, else the one h."""
-        return self.hbuf[l & 1] if self._fused else self.h
+        return self.hbuf[l % self._nbuf] if (self._fused or self._stream) else self.h
 
     def _build_plans(self, M: int):
         """One grouped-launch plan per layer: q, k, v, gate, up store their outputs; o and down add
@@ -208,6 +223,11 @@ class LayerStack:
         self._plans, self._plan_mem = [], []
         self._ep_counter = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._own_h = torch.tensor([self.h.data_ptr()], dtype=torch.int64, device=self.device)
+        if self._stream:
+            self._tile_cnt = torch.zeros((cfg.hidden // g + 31) // 32, dtype=torch.int32, device=self.device)
+            if not self._fused:
+                self._own_hbuf = [torch.tensor([self.hbuf[p].data_ptr()], dtype=torch.int64, device=self.device)
+                                  for p in range(self._nbuf)]
         for l in range(self.layers):
             descs = (N.Linear4Desc * 7)()
             for i, pr in enumerate(self.proj[l]):
@@ -235,11 +255,14 @@ class LayerStack:
                 ep = plan.ep
                 ep.acc, ep.alpha, ep.counter = self.acc.data_ptr(), self.alpha, self._ep_counter.data_ptr()
                 ep.M, ep.hs, ep.H, ep.rank, ep.nranks = M, cfg.hidden // g, cfg.hidden, self.rank, g
+                nxt = (l + 1) % self._nbuf
                 if self._fused:
-                    ep.peer_h, ep.peer_flags = self._peer_h[(l + 1) & 1].data_ptr(), self._peer_flags.data_ptr()
+                    ep.peer_h, ep.peer_flags = self._peer_h[nxt].data_ptr(), self._peer_flags.data_ptr()
                     ep.step, ep.mul, ep.add = self.step_ctr.data_ptr(), self.layers, l + 1
                 else:
-                    ep.peer_h = self._own_h.data_ptr()
+                    ep.peer_h = self._own_hbuf[nxt].data_ptr() if self._stream else self._own_h.data_ptr()
+                if self._stream:
+                    ep.tile_cnt, ep.tile_expect = self._tile_cnt.data_ptr(), plan.acc_parts
             if self._fused:
                 # layer 0 waits for the acks of the previous step (every rank has copied its result out), the
                 # others for the boundary flags of the layer before
@@ -274,14 +297,14 @@ class LayerStack:
                     continue
                 N.check(lib.mpsbnb_stack_boundary_push(N.ptr(self.acc), C.c_float(self.alpha), N.i64(M), N.i64(hs),
                                                        N.i64(cfg.hidden), C.c_int(self.rank), C.c_int(g),
-                                                       N.ptr(self._peer_h[(l + 1) & 1]), N.ptr(self._peer_flags),
+                                                       N.ptr(self._peer_h[(l + 1) % self._nbuf]), N.ptr(self._peer_flags),
                                                        N.ptr(self.step_ctr), C.c_int(L), C.c_int(l + 1), N.dt(self.dtype),
                                                        C.c_int(N.GROUP_PDL), N.stream()), "stack_boundary_push")
             # the step is complete here once every rank's last shard has landed; keep the result in a buffer no
             # peer writes, then tell the peers (acks) that this rank's h buffers may be overwritten again
             N.check(lib.mpsbnb_flags_wait(N.ptr(self.flags), C.c_int(g), N.ptr(self.step_ctr), C.c_int(L), C.c_int(L),
                                           C.c_int(1), N.stream()), "flags_wait")
-            self.h_out.copy_(self.hbuf[L & 1])
+            self.h_out.copy_(self.hbuf[L % self._nbuf])
             N.check(lib.mpsbnb_counter_add(N.ptr(self.step_ctr), C.c_int(1), N.stream()), "counter_add")
             N.check(lib.mpsbnb_flags_push(N.ptr(self._peer_acks), C.c_int(self.rank), C.c_int(g), N.ptr(self.step_ctr),
                                           C.c_int(1), C.c_int(0), N.stream()), "flags_push")
@@ -364,11 +387,16 @@ class LayerStack:
             else:
                 self._load_input()
                 self._run_layers(self._M)
-        return self.h_out if self._fused else self.h
+        return self._result()
+
+    def _result(self) -> torch.Tensor:
+        if self._fused:
+            return self.h_out
+        return self.hbuf[self.layers % self._nbuf] if self._stream else self.h
 
     def output(self) -> torch.Tensor:
         """h after the last layer of the latest step."""
-        return self.h_out if self._fused else self.h
+        return self._result()
 
     def launches_per_step(self) -> int:
         """Kernels of this library launched per step (NCCL's own kernels not counted)."""

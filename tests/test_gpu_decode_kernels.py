@@ -61,7 +61,7 @@ def test_tcgen05_kernel_grouped_stack(tcgen05_kernel, M):
     """The grouped launch cuts row tiles between CTAs (fp32 workspace + arrival counters): three layers, graph
     replayed twice, so the workspace has to come back to zero every time."""
     cfg = S.StackConfig("tiny", hidden=256, ffn=704, kv=64, layers=3)
-    st = S.LayerStack(cfg, device="cuda:0", quant_type="nf4", double_quant=True, seed=5, in_kernel_boundary=False)
+    st = S.LayerStack(cfg, device="cuda:0", quant_type="nf4", double_quant=True, seed=5, boundary="kernel")
     x = np.random.default_rng(M).standard_normal((M, cfg.hidden)).astype(np.float16)
     st.prepare(M, use_graph=True)
     ref_h, ref_out = oracle_stack(st, x)

@@ -28,12 +28,14 @@ def oracle_stack(st: S.LayerStack, x: np.ndarray):
     return h, outs
 
 
-@pytest.mark.parametrize("M,in_kernel", [(1, True), (1, False), (3, True), (8, True), (8, False), (16, True)])
+@pytest.mark.parametrize("M,boundary", [(1, "kernel"), (1, "inline"), (1, "stream"), (3, "inline"), (3, "stream"),
+                                        (8, "kernel"), (8, "stream"), (16, "kernel")])
 @pytest.mark.parametrize("qt,dq", [("nf4", True), ("fp4", False)])
-def test_small_stack_matches_oracle(M, in_kernel, qt, dq):
-    """in_kernel: the layer boundary is the closing step of the grouped GEMV launch; otherwise its own kernel."""
+def test_small_stack_matches_oracle(M, boundary, qt, dq):
+    """boundary: the layer boundary as its own kernel, as the closing step of the grouped GEMV launch (last CTA), or
+    streamed tile by tile from inside the launch."""
     cfg = S.StackConfig("tiny", hidden=256, ffn=704, kv=64, layers=3)
-    st = S.LayerStack(cfg, device="cuda:0", quant_type=qt, double_quant=dq, seed=5, in_kernel_boundary=in_kernel)
+    st = S.LayerStack(cfg, device="cuda:0", quant_type=qt, double_quant=dq, seed=5, boundary=boundary)
     rng = np.random.default_rng(M)
     x = rng.standard_normal((M, cfg.hidden)).astype(np.float16)
     for use_graph in (False, True):

@@ -11,7 +11,7 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def _worker(rank, world, port, M, fused):
+def _worker(rank, world, port, M, fused, boundary):
     import torch.distributed as dist
     from mps_bitsandbytes_b200 import stack as S
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
@@ -22,7 +22,7 @@ def _worker(rank, world, port, M, fused):
     whole = S.LayerStack(cfg, device=f"cuda:{rank}", seed=21)                   # the same model on every rank
     whole.prepare(M, use_graph=False)
     ref = whole.step(x).float().clone()
-    part = S.LayerStack(cfg, device=f"cuda:{rank}", seed=21, rank=rank, world=world, fused_exchange=fused)
+    part = S.LayerStack(cfg, device=f"cuda:{rank}", seed=21, rank=rank, world=world, fused_exchange=fused, boundary=boundary)
     ok = True
     for use_graph in (False, True):
         part.prepare(M, use_graph=use_graph)
@@ -43,8 +43,9 @@ def _worker(rank, world, port, M, fused):
     os._exit(0 if int(flag.item()) == 1 else 1)
 
 
-@pytest.mark.parametrize("M,fused", [(1, True), (4, True), (1, False), (16, True)])
-def test_two_rank_stack_matches_single_gpu(M, fused):
+@pytest.mark.parametrize("M,fused,boundary", [(1, True, "kernel"), (4, True, "inline"), (1, True, "stream"), (8, True, "stream"),
+                                              (1, False, "kernel"), (16, True, "kernel")])
+def test_two_rank_stack_matches_single_gpu(M, fused, boundary):
     """fused: peer stores + flags at the layer boundary (batch <= 8); otherwise NCCL all-gather."""
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
@@ -52,7 +53,7 @@ def test_two_rank_stack_matches_single_gpu(M, fused):
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
         port = s.getsockname()[1]
-    ctx = mp.spawn(_worker, args=(2, port, M, fused), nprocs=2, join=False)
+    ctx = mp.spawn(_worker, args=(2, port, M, fused, boundary), nprocs=2, join=False)
     # bounded: a rank that never joins must not hold the suite
     for p in ctx.processes:
         p.join(timeout=180)
