@@ -442,11 +442,47 @@ __global__ void __launch_bounds__(SG_THREADS, 1) gemv4_stream_kernel(const __gri
         const int wrt = lane >> 4;
         pdl_grid_dependency_wait();                              // outputs may still be read by the previous kernel
         int uc = 0;
+        int pend_tile = -1, pend_old = 0;
+        // whoever brought the last contribution of a tile converts it, stores it into every rank's h, re-arms the
+        // accumulator, and - after the last tile of the shard - raises the flags
+        auto resolve_pending = [&]() {
+            if (pend_tile < 0) return;
+            const int old = __shfl_sync(0xffffffffu, pend_old, 0);
+            const int tile = pend_tile;
+            pend_tile = -1;
+            if (old != a.ep.tile_expect - 1) return;
+            __threadfence();
+            XT *const *peers = reinterpret_cast<XT *const *>(a.ep.peer_h);
+            const int n = tile * SG_ROWS + lane;
+            if (n < a.ep.hs) {
+                for (int m = 0; m < a.M; ++m) {
+                    float *pa = a.ep.acc + (int64_t)m * a.ep.hs + n;
+                    const XT hv = from_f32<XT>(a.ep.alpha * __ldcg(pa));
+                    *pa = 0.0f;
+                    const int64_t o = (int64_t)m * a.ep.H + (int64_t)a.ep.rank * a.ep.hs + n;
+                    for (int r = 0; r < a.ep.nranks; ++r) peers[r][o] = hv;
+                }
+            }
+            if (lane == 0) a.ep.tile_cnt[tile] = 0;
+            __threadfence_system();
+            __syncwarp();
+            int done = 0;
+            if (lane == 0) done = atomicAdd(a.ep.counter, 1);
+            done = __shfl_sync(0xffffffffu, done, 0);
+            if (done == (a.ep.hs + SG_ROWS - 1) / SG_ROWS - 1) {
+                // every tile of this rank's shard has been stored (each store was fenced before its count)
+                __threadfence_system();
+                if (lane == 0) *a.ep.counter = 0;
+                if (a.ep.peer_flags != nullptr && lane < a.ep.nranks)
+                    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(a.ep.peer_flags[lane] + a.ep.rank), "r"((*a.ep.step) * a.ep.mul + a.ep.add) : "memory");
+            }
+        };
         for (int u = blockIdx.x; u < a.nunits && !*abort_flag; u += gridDim.x, ++uc) {
             const StreamUnit un = unit_of(u);
             const StreamLinear *L = lin_of(un.lin);
             const int buf = uc & 1;
             if (!mbar_wait_sleep(red_full(buf), (uint32_t)(uc >> 1) & 1u, abort_flag, a.sleep_other)) { atomicExch(&g_stream_status, 204); *abort_flag = 1; break; }
+            resolve_pending();                                   // the count issued one unit ago has long returned
             const float *red = reinterpret_cast<const float *>(p_generic0 + s_red + buf * SG_RED_BYTES);
             const int n = un.row0 + lane;
             for (int m = 0; m < a.M; ++m) {
@@ -471,42 +507,16 @@ __global__ void __launch_bounds__(SG_THREADS, 1) gemv4_stream_kernel(const __gri
             __syncwarp();
             if (lane == 0) mbar_arrive(red_empty(buf));
             if (a.ep.tile_cnt != nullptr && L->acc == a.ep.acc && L->acc != nullptr) {
-                // streamed closing step: count this unit's contribution to its 32-row tile; whoever brings the
-                // last one converts the tile, stores it into every rank's h and re-arms the accumulator
-                __threadfence();
+                // streamed closing step: count this unit's contribution to its 32-row tile.  The count is a release
+                // (it orders this warp's accumulator updates before it) and its result is looked at one unit
+                // later, so the round trip never stalls this warp.
                 __syncwarp();
-                const int tile = un.row0 / SG_ROWS;
-                int old = 0;
-                if (lane == 0) old = atomicAdd(a.ep.tile_cnt + tile, 1);
-                old = __shfl_sync(0xffffffffu, old, 0);
-                if (old == a.ep.tile_expect - 1) {
-                    __threadfence();
-                    XT *const *peers = reinterpret_cast<XT *const *>(a.ep.peer_h);
-                    if (n < a.ep.hs) {
-                        for (int m = 0; m < a.M; ++m) {
-                            float *pa = a.ep.acc + (int64_t)m * a.ep.hs + n;
-                            const XT hv = from_f32<XT>(a.ep.alpha * __ldcg(pa));
-                            *pa = 0.0f;
-                            const int64_t o = (int64_t)m * a.ep.H + (int64_t)a.ep.rank * a.ep.hs + n;
-                            for (int r = 0; r < a.ep.nranks; ++r) peers[r][o] = hv;
-                        }
-                    }
-                    if (lane == 0) a.ep.tile_cnt[tile] = 0;
-                    __threadfence_system();
-                    __syncwarp();
-                    int done = 0;
-                    if (lane == 0) done = atomicAdd(a.ep.counter, 1);
-                    done = __shfl_sync(0xffffffffu, done, 0);
-                    if (done == (a.ep.hs + SG_ROWS - 1) / SG_ROWS - 1) {
-                        // every tile of this rank's shard has been stored (each store was fenced before its count)
-                        __threadfence_system();
-                        if (lane == 0) *a.ep.counter = 0;
-                        if (a.ep.peer_flags != nullptr && lane < a.ep.nranks)
-                            asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(a.ep.peer_flags[lane] + a.ep.rank), "r"((*a.ep.step) * a.ep.mul + a.ep.add) : "memory");
-                    }
-                }
+                pend_tile = un.row0 / SG_ROWS;
+                if (lane == 0)
+                    asm volatile("atom.add.release.gpu.global.s32 %0, [%1], 1;" : "=r"(pend_old) : "l"(a.ep.tile_cnt + pend_tile) : "memory");
             }
         }
+        resolve_pending();
         __threadfence();                                         // my results before this CTA's arrival at the closing step
     } else if (warp > SG_CONSUMERS) {
         // ------------------------------------------------------------ loaders: block scales and x into the scale/x ring
