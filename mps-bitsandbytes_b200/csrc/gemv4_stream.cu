@@ -46,7 +46,8 @@ constexpr int SG_GROUPS = 4;                             // independent consumer
 constexpr int SG_GROUP_WARPS = SG_CONSUMERS / SG_GROUPS;
 constexpr int SG_ITEMS = 8 / (SG_GROUP_WARPS / 2);       // block pairs a warp works through per stage
 constexpr int SG_LOADERS = 4;                           // must equal SG_MAX_XS (see there)
-constexpr int SG_THREADS = (SG_CONSUMERS + 1 + SG_LOADERS + 1) * 32;   // + TMA warp + reducer warp
+constexpr int SG_THREADS = (SG_CONSUMERS + 1 + SG_LOADERS + 2) * 32;   // + TMA warp + reducer warp + closer warp
+constexpr int SG_MAIL = 4;                               // mailbox entries between reducer and closer
 constexpr int SG_ROWS = 32;                              // weight rows per unit
 constexpr int SG_STAGE_BLOCKS = 16;                      // quantisation blocks (of 64 k) per stage
 constexpr int SG_W_BYTES = SG_ROWS * SG_STAGE_BLOCKS * 32;   // 16384 packed bytes per stage
@@ -257,6 +258,7 @@ __device__ __forceinline__ uint4 lds128v(uint32_t addr) {
     asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
     return v;
 }
+__device__ __forceinline__ uint32_t lds_u32v(uint32_t addr) { uint32_t v; asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory"); return v; }
 __device__ __forceinline__ float lds_f32v(uint32_t addr) { float v; asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory"); return v; }
 // the table never changes after the prologue: the compiler may schedule this load freely
 __device__ __forceinline__ uint32_t lut_pair(uint32_t addr) { uint32_t v; asm("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr)); return v; }
@@ -343,7 +345,11 @@ __global__ void __launch_bounds__(SG_THREADS, 1) gemv4_stream_kernel(const __gri
 
     const int nxs = a.M <= 2 ? SG_MAX_XS : 4;                        // scale/x slots (released after the MMAs)
     const uint32_t xs_bytes = (uint32_t)(SG_A_BYTES + ((a.M * SG_XPITCH + 127) / 128) * 128);
-    const uint32_t s_xs = (s_bar + 384u + 127u) & ~127u;
+    // mailbox reducer -> closer: full[4] empty[4] barriers at +352, the tile indices at +416
+    auto mail_full = [&](int i) { return s_bar + 352u + 8u * i; };
+    auto mail_empty = [&](int i) { return s_bar + 352u + 8u * (SG_MAIL + i); };
+    const uint32_t s_mail = s_bar + 416u;
+    const uint32_t s_xs = (s_bar + 512u + 127u) & ~127u;
     SlotMap sm;
     sm.low0 = (s_xs + (uint32_t)nxs * xs_bytes + 1023u) & ~1023u;
     sm.high0 = SG_HIGH_ABS;
@@ -371,6 +377,7 @@ __global__ void __launch_bounds__(SG_THREADS, 1) gemv4_stream_kernel(const __gri
     if (tid == 0) {
         for (int s = 0; s < nslots; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), SG_GROUP_WARPS); }
         for (int b = 0; b < 2; ++b) { mbar_init(red_full(b), SG_CONSUMERS); mbar_init(red_empty(b), 1); }
+        for (int i = 0; i < SG_MAIL; ++i) { mbar_init(mail_full(i), 1); mbar_init(mail_empty(i), 1); }
         for (int s = 0; s < nxs; ++s) { mbar_init(xfull_bar(s), 1); mbar_init(xempty_bar(s), SG_GROUP_WARPS); }
         *abort_flag = 0;
         fence_mbar_init();
@@ -443,39 +450,21 @@ __global__ void __launch_bounds__(SG_THREADS, 1) gemv4_stream_kernel(const __gri
         pdl_grid_dependency_wait();                              // outputs may still be read by the previous kernel
         int uc = 0;
         int pend_tile = -1, pend_old = 0;
-        // whoever brought the last contribution of a tile converts it, stores it into every rank's h, re-arms the
-        // accumulator, and - after the last tile of the shard - raises the flags
+        // whoever brought the last contribution of a tile hands the tile to the closer warp (mailbox), which
+        // converts it, stores it into every rank's h and re-arms the accumulator without holding this warp up
+        int mail_i = 0; uint32_t mail_ph = 0;
+        auto post = [&](int tile) {
+            if (!mbar_wait_sleep(mail_empty(mail_i), mail_ph ^ 1u, abort_flag, a.sleep_other)) { atomicExch(&g_stream_status, 208); *abort_flag = 1; return; }
+            if (lane == 0) { sts32(s_mail + 4u * mail_i, (uint32_t)tile); mbar_arrive(mail_full(mail_i)); }
+            __syncwarp();
+            if (++mail_i == SG_MAIL) { mail_i = 0; mail_ph ^= 1u; }
+        };
         auto resolve_pending = [&]() {
             if (pend_tile < 0) return;
             const int old = __shfl_sync(0xffffffffu, pend_old, 0);
             const int tile = pend_tile;
             pend_tile = -1;
-            if (old != a.ep.tile_expect - 1) return;
-            __threadfence();
-            XT *const *peers = reinterpret_cast<XT *const *>(a.ep.peer_h);
-            const int n = tile * SG_ROWS + lane;
-            if (n < a.ep.hs) {
-                for (int m = 0; m < a.M; ++m) {
-                    float *pa = a.ep.acc + (int64_t)m * a.ep.hs + n;
-                    const XT hv = from_f32<XT>(a.ep.alpha * __ldcg(pa));
-                    *pa = 0.0f;
-                    const int64_t o = (int64_t)m * a.ep.H + (int64_t)a.ep.rank * a.ep.hs + n;
-                    for (int r = 0; r < a.ep.nranks; ++r) peers[r][o] = hv;
-                }
-            }
-            if (lane == 0) a.ep.tile_cnt[tile] = 0;
-            __threadfence_system();
-            __syncwarp();
-            int done = 0;
-            if (lane == 0) done = atomicAdd(a.ep.counter, 1);
-            done = __shfl_sync(0xffffffffu, done, 0);
-            if (done == (a.ep.hs + SG_ROWS - 1) / SG_ROWS - 1) {
-                // every tile of this rank's shard has been stored (each store was fenced before its count)
-                __threadfence_system();
-                if (lane == 0) *a.ep.counter = 0;
-                if (a.ep.peer_flags != nullptr && lane < a.ep.nranks)
-                    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(a.ep.peer_flags[lane] + a.ep.rank), "r"((*a.ep.step) * a.ep.mul + a.ep.add) : "memory");
-            }
+            if (old == a.ep.tile_expect - 1) post(tile);
         };
         for (int u = blockIdx.x; u < a.nunits && !*abort_flag; u += gridDim.x, ++uc) {
             const StreamUnit un = unit_of(u);
@@ -517,7 +506,46 @@ __global__ void __launch_bounds__(SG_THREADS, 1) gemv4_stream_kernel(const __gri
             }
         }
         resolve_pending();
+        if (a.ep.tile_cnt != nullptr && !*abort_flag) post(-1);    // tells the closer warp that nothing more will come
         __threadfence();                                         // my results before this CTA's arrival at the closing step
+    } else if (warp == SG_CONSUMERS + 2 + SG_LOADERS) {
+        // ------------------------------------------------------------ closer (streamed closing step only)
+        if (a.ep.tile_cnt != nullptr) {
+            XT *const *peers = reinterpret_cast<XT *const *>(a.ep.peer_h);
+            int mi = 0; uint32_t mph = 0;
+            while (!*abort_flag) {
+                if (!mbar_wait_sleep(mail_full(mi), mph, abort_flag, a.sleep_other)) { atomicExch(&g_stream_status, 209); *abort_flag = 1; break; }
+                const int tile = (int)lds_u32v(s_mail + 4u * mi);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(mail_empty(mi));
+                if (++mi == SG_MAIL) { mi = 0; mph ^= 1u; }
+                if (tile < 0) break;
+                __threadfence();                                 // the contributions were counted with release atomics
+                const int n = tile * SG_ROWS + lane;
+                if (n < a.ep.hs) {
+                    for (int m = 0; m < a.M; ++m) {
+                        float *pa = a.ep.acc + (int64_t)m * a.ep.hs + n;
+                        const XT hv = from_f32<XT>(a.ep.alpha * __ldcg(pa));
+                        *pa = 0.0f;
+                        const int64_t o = (int64_t)m * a.ep.H + (int64_t)a.ep.rank * a.ep.hs + n;
+                        for (int r = 0; r < a.ep.nranks; ++r) peers[r][o] = hv;
+                    }
+                }
+                if (lane == 0) a.ep.tile_cnt[tile] = 0;
+                if (a.ep.nranks > 1) __threadfence_system(); else __threadfence();   // the stores before the count
+                __syncwarp();
+                int done = 0;
+                if (lane == 0) done = atomicAdd(a.ep.counter, 1);
+                done = __shfl_sync(0xffffffffu, done, 0);
+                if (done == (a.ep.hs + SG_ROWS - 1) / SG_ROWS - 1) {
+                    // every tile of this rank's shard has been stored (each store was fenced before its count)
+                    if (a.ep.nranks > 1) __threadfence_system(); else __threadfence();
+                    if (lane == 0) *a.ep.counter = 0;
+                    if (a.ep.peer_flags != nullptr && lane < a.ep.nranks)
+                        asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(a.ep.peer_flags[lane] + a.ep.rank), "r"((*a.ep.step) * a.ep.mul + a.ep.add) : "memory");
+                }
+            }
+        }
     } else if (warp > SG_CONSUMERS) {
         // ------------------------------------------------------------ loaders: block scales and x into the scale/x ring
         // SG_LOADERS warps take stages in turn; each reads the scales of its NEXT stage before it stores
