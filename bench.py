@@ -216,7 +216,7 @@ def run_gpu(args, cfg):
     peaks = load_peaks()
     M = args.batch
     stack = S.LayerStack(cfg, device=f"cuda:{local}", rank=rank, world=world, layers=args.layers,
-                         fused_exchange=args.exchange == "fused", boundary=args.boundary)
+                         fused_exchange=args.exchange == "fused", boundary=args.boundary, persistent=args.one_launch and not args.per_layer)
     stack.prepare(M, use_graph=True)
     gen = torch.Generator(device="cpu"); gen.manual_seed(1)
     x_host = torch.randn(M, cfg.hidden, generator=gen).half().pin_memory()
@@ -270,8 +270,9 @@ def run_gpu(args, cfg):
     if rank == 0:
         per_gpu = gbs / world
         grouped = stack._plans is not None
-        n_gemv = stack.layers if grouped else 7 * stack.layers
-        kname = "gemv4_stream_kernel (one launch per layer: 7 linears)" if grouped else "gemv4_kernel (one launch per linear)"
+        n_gemv = len(stack._plans) if grouped else 7 * stack.layers
+        kname = ("gemv4_stream_kernel (one cooperative launch per step: all layers)" if grouped and n_gemv == 1 and stack.layers > 1
+                 else "gemv4_stream_kernel (one launch per layer: 7 linears)" if grouped else "gemv4_kernel (one launch per linear)")
         out = {
             "metric": "nf4_decode_gbs", "value": gbs, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
@@ -279,7 +280,8 @@ def run_gpu(args, cfg):
             "config": dict(workload_config(cfg, M, stack.layers, world), outputs_finite=finite),
             "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                          "frac": per_gpu / peaks["hbm_gbs"],
-                         "traffic": NCU_TRAFFIC_7B_LAYER_BYTES if (grouped and world == 1 and M == 1 and cfg.name == "llama2-7b") else None,
+                         "traffic": NCU_TRAFFIC_7B_LAYER_BYTES * (stack.layers if n_gemv == 1 else 1)
+                         if (grouped and world == 1 and M == 1 and cfg.name == "llama2-7b") else None,
                          "peak_source": peaks["source"],
                          "kernel": kname, "launches_per_step": n_gemv,
                          "bytes_per_launch": nbytes / world / n_gemv,
@@ -324,8 +326,10 @@ def main():
     ap.add_argument("--exchange", default="fused", choices=["fused", "nccl"],
                     help="N > 1: layer boundary by peer stores + flags (default) or by an NCCL all-gather")
     ap.add_argument("--boundary", default=None, choices=["kernel", "inline", "stream"],
-                    help="layer boundary: its own small kernel (default on one GPU), the closing step of the GEMV "
-                         "launch, or streamed tile by tile from inside the launch (default with the fused exchange)")
+                    help="layer boundary: its own small kernel, the closing step of the GEMV launch, or streamed tile "
+                         "by tile from inside the launch (default)")
+    ap.add_argument("--per-layer", action="store_true", help="one GEMV launch per layer instead of one per step")
+    ap.add_argument("--one-launch", action="store_true", help="one cooperative GEMV launch per step (all layers)")
     args = ap.parse_args()
     from mps_bitsandbytes_b200 import stack as S
     cfg = S.LLAMA2_7B if args.model == "llama2-7b" else S.LLAMA_70B

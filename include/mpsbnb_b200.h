@@ -126,6 +126,8 @@ typedef struct mpsbnb_linear4_desc {
     void *y;
     float *acc;
     int64_t N, K;
+    int64_t segment;          /* 0, 1, 2 ...: linears of segment g + 1 read what the closing step of segment g wrote
+                               * (several decoder layers in ONE launch); all 0 for an ordinary group */
 } mpsbnb_linear4_desc;
 
 /* Two kernels implement the M <= 8 decode path.  0 (default): TMA ring, table expansion, dot
@@ -148,7 +150,13 @@ int mpsbnb_decode_kernel_select(int which);
  * are raised after the last tile.  Linears with an accumulator are scheduled first in a launch, so this
  * happens early and the exchange hides behind the rest of the launch.  Because h of the NEXT layer is
  * then written while THIS layer is still reading its own h, peer_h must not be the buffer the launch reads
- * x from (rotate three buffers when ranks may run more than a layer apart). */
+ * x from (rotate three buffers when ranks may run more than a layer apart).
+ * Several segments in one launch (mpsbnb_linear4_desc.segment; streamed form only): the closing step of
+ * segment g stores into buffer (g + 1) % nbuf — peer_h is then an array of nbuf * nranks pointers,
+ * [buffer][rank] — and raises the flags to (*step) * mul + add + g; linears of segment g >= 1 wait
+ * (plan.wait_*) until all flags are >= (*wait_step) * wait_mul + wait_add + g.  One accumulator and one
+ * tile_cnt serve all segments (segment g + 1 cannot add before segment g is closed).  Such a launch is
+ * cooperative: all its CTAs are resident, because CTAs wait for each other's closing steps. */
 typedef struct mpsbnb_group_epilogue {
     float *acc;
     void *const *peer_h;
@@ -158,6 +166,7 @@ typedef struct mpsbnb_group_epilogue {
     int *tile_cnt;
     float alpha;
     int M, hs, H, rank, nranks, mul, add, tile_expect;
+    int nbuf, pad_;           /* buffers peer_h rotates over (0 or 1: a single one) */
 } mpsbnb_group_epilogue;
 
 typedef struct mpsbnb_group_plan {
@@ -173,7 +182,8 @@ typedef struct mpsbnb_group_plan {
     const int *wait_flags;
     const int *wait_step;
     int wait_n, wait_mul, wait_add;
-    int acc_parts;            /* filled by the plan call: units per 32-row tile that add into an accumulator */
+    int acc_parts;            /* filled by the plan call: units per 32-row tile and segment that add into an accumulator */
+    int n_segments, pad_;     /* filled by the plan call */
     mpsbnb_group_epilogue ep; /* optional, set by the caller before a run (default kernel only) */
 } mpsbnb_group_plan;
 

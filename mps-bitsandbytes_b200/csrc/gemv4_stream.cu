@@ -77,7 +77,7 @@ struct StreamLinear {
     int x_vec_ok;             // 16-byte loads of x are legal
     int x_bulk_ok;            // every stage's x columns are one 16-byte-aligned contiguous run: TMA bulk copies
     int map3d;                // map is {128 B, N rows, row_bytes / 128}: one box {128, 32, 4} fetches a whole stage
-    int pad_;
+    int segment;              // linears of segment g + 1 read what the closing step of segment g wrote
 };
 
 struct StreamUnit { int lin, row0, s_begin, s_end; };
@@ -449,7 +449,7 @@ __global__ void __launch_bounds__(SG_THREADS, 1) gemv4_stream_kernel(const __gri
         const int wrt = lane >> 4;
         pdl_grid_dependency_wait();                              // outputs may still be read by the previous kernel
         int uc = 0;
-        int pend_tile = -1, pend_old = 0;
+        int pend_tile = -1, pend_old = 0;                        // pend_tile: segment << 16 | tile
         // whoever brought the last contribution of a tile hands the tile to the closer warp (mailbox), which
         // converts it, stores it into every rank's h and re-arms the accumulator without holding this warp up
         int mail_i = 0; uint32_t mail_ph = 0;
@@ -500,9 +500,9 @@ __global__ void __launch_bounds__(SG_THREADS, 1) gemv4_stream_kernel(const __gri
                 // (it orders this warp's accumulator updates before it) and its result is looked at one unit
                 // later, so the round trip never stalls this warp.
                 __syncwarp();
-                pend_tile = un.row0 / SG_ROWS;
+                pend_tile = (L->segment << 16) | (un.row0 / SG_ROWS);
                 if (lane == 0)
-                    asm volatile("atom.add.release.gpu.global.s32 %0, [%1], 1;" : "=r"(pend_old) : "l"(a.ep.tile_cnt + pend_tile) : "memory");
+                    asm volatile("atom.add.release.gpu.global.s32 %0, [%1], 1;" : "=r"(pend_old) : "l"(a.ep.tile_cnt + un.row0 / SG_ROWS) : "memory");
             }
         }
         resolve_pending();
@@ -511,15 +511,18 @@ __global__ void __launch_bounds__(SG_THREADS, 1) gemv4_stream_kernel(const __gri
     } else if (warp == SG_CONSUMERS + 2 + SG_LOADERS) {
         // ------------------------------------------------------------ closer (streamed closing step only)
         if (a.ep.tile_cnt != nullptr) {
-            XT *const *peers = reinterpret_cast<XT *const *>(a.ep.peer_h);
+            XT *const *all_peers = reinterpret_cast<XT *const *>(a.ep.peer_h);
+            const int nbuf = a.ep.nbuf > 1 ? a.ep.nbuf : 1;
             int mi = 0; uint32_t mph = 0;
             while (!*abort_flag) {
                 if (!mbar_wait_sleep(mail_full(mi), mph, abort_flag, a.sleep_other)) { atomicExch(&g_stream_status, 209); *abort_flag = 1; break; }
-                const int tile = (int)lds_u32v(s_mail + 4u * mi);
+                const int word = (int)lds_u32v(s_mail + 4u * mi);
                 __syncwarp();
                 if (lane == 0) mbar_arrive(mail_empty(mi));
                 if (++mi == SG_MAIL) { mi = 0; mph ^= 1u; }
-                if (tile < 0) break;
+                if (word < 0) break;
+                const int seg = word >> 16, tile = word & 0xFFFF;
+                XT *const *peers = all_peers + (nbuf > 1 ? ((seg + 1) % nbuf) * a.ep.nranks : 0);
                 __threadfence();                                 // the contributions were counted with release atomics
                 const int n = tile * SG_ROWS + lane;
                 if (n < a.ep.hs) {
@@ -542,7 +545,7 @@ __global__ void __launch_bounds__(SG_THREADS, 1) gemv4_stream_kernel(const __gri
                     if (a.ep.nranks > 1) __threadfence_system(); else __threadfence();
                     if (lane == 0) *a.ep.counter = 0;
                     if (a.ep.peer_flags != nullptr && lane < a.ep.nranks)
-                        asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(a.ep.peer_flags[lane] + a.ep.rank), "r"((*a.ep.step) * a.ep.mul + a.ep.add) : "memory");
+                        asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(a.ep.peer_flags[lane] + a.ep.rank), "r"((*a.ep.step) * a.ep.mul + a.ep.add + seg) : "memory");
                 }
             }
         }
@@ -552,24 +555,6 @@ __global__ void __launch_bounds__(SG_THREADS, 1) gemv4_stream_kernel(const __gri
         // the current one, so two rounds of global loads are in flight per warp.
         const int me = warp - SG_CONSUMERS - 1;
         pdl_grid_dependency_wait();                              // x is written by the previous kernel in the stream
-        if (a.wait_n > 0) {
-            // ... and, in the N-sharded stack, by the boundary kernels of the other GPUs: wait (bounded) for their flags
-            const int expect = (*a.wait_step) * a.wait_mul + a.wait_add;
-            bool arrived = true;
-            if (lane < a.wait_n) {
-                const long long t0 = clock64();
-                for (;;) {
-                    int v;
-                    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(a.wait_flags + lane) : "memory");
-                    if (v >= expect) break;
-                    __nanosleep(64);
-                    if (*abort_flag != 0 || clock64() - t0 > 2000000000ll) { arrived = false; break; }
-                }
-            }
-            arrived = __all_sync(0xffffffffu, arrived);
-            asm volatile("fence.proxy.async;" ::: "memory");      // x is then read by bulk copies (async proxy)
-            if (!arrived) { atomicExch(&g_stream_status, 207); *abort_flag = 1; }
-        }
         {
             auto read_scales = [&](const StreamLinear *L, int row0, int s, float (&sc)[16]) {
                 const int n = row0 + lane;
@@ -640,6 +625,7 @@ __global__ void __launch_bounds__(SG_THREADS, 1) gemv4_stream_kernel(const __gri
                 }
             };
             float cur[16];
+            int ready_seg = -1;                  // segments whose input is known to be complete
             bool more = advance_to_mine();
             if (more) read_scales(L, un.row0, s, cur);
             while (more && !*abort_flag) {
@@ -652,6 +638,26 @@ __global__ void __launch_bounds__(SG_THREADS, 1) gemv4_stream_kernel(const __gri
                 if (more) read_scales(L, un.row0, s, nxt);
                 if (!mbar_wait_sleep(xempty_bar(my_x), my_ph ^ 1u, abort_flag, a.sleep_other)) { atomicExch(&g_stream_status, 202); *abort_flag = 1; break; }
                 const uint32_t xb = s_xs + (uint32_t)my_x * xs_bytes;
+                if (a.wait_n > 0 && my_L->segment > ready_seg) {
+                    // x of this segment is written by closing steps: of the previous launch or segment, on this GPU and,
+                    // in the N-sharded stack, on the others.  Wait (bounded) for their flags.
+                    const int expect = (*a.wait_step) * a.wait_mul + a.wait_add + my_L->segment;
+                    bool arrived = true;
+                    if (lane < a.wait_n) {
+                        const long long t0 = clock64();
+                        for (;;) {
+                            int v;
+                            asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(a.wait_flags + lane) : "memory");
+                            if (v >= expect) break;
+                            __nanosleep(64);
+                            if (*abort_flag != 0 || clock64() - t0 > 2000000000ll) { arrived = false; break; }
+                        }
+                    }
+                    arrived = __all_sync(0xffffffffu, arrived);
+                    asm volatile("fence.proxy.async;" ::: "memory");      // x is then read by bulk copies (async proxy)
+                    if (!arrived) { atomicExch(&g_stream_status, 207); *abort_flag = 1; break; }
+                    ready_seg = my_L->segment;
+                }
 #pragma unroll
                 for (int j = 0; j < 16; ++j) sts_f32(xb + (j * 32 + lane) * 4, cur[j]);
                 int xcols = my_L->K - my_s * (SG_STAGE_BLOCKS * 64);
@@ -680,7 +686,8 @@ __global__ void __launch_bounds__(SG_THREADS, 1) gemv4_stream_kernel(const __gri
                             uint16_t e[8];
 #pragma unroll
                             for (int j = 0; j < 8; ++j)
-                                e[j] = (k0 + j < my_L->K) ? *reinterpret_cast<const uint16_t *>(xr + (k0 + j) % my_L->x_period) : (uint16_t)0;
+                                e[j] = (k0 + j < my_L->K) ? __ldcg(reinterpret_cast<const unsigned short *>(xr + (k0 + j) % my_L->x_period))
+                                                          : (unsigned short)0;    // L2 only: x may have been written during this launch
                             sts128(xb + SG_A_BYTES + m * SG_XPITCH + (lane + 32 * c4) * 16,
                                    make_uint4(e[0] | ((uint32_t)e[1] << 16), e[2] | ((uint32_t)e[3] << 16),
                                               e[4] | ((uint32_t)e[5] << 16), e[6] | ((uint32_t)e[7] << 16)));
@@ -906,7 +913,7 @@ static EncodeTiledFn encode_tiled() {
 
 struct HostLinear {
     const void *x; int64_t x_ld; int64_t x_period; const uint8_t *packed; const void *absmax; const float *absmax2;
-    const void *bias; void *y; float *acc; int64_t N, K;
+    const void *bias; void *y; float *acc; int64_t N, K; int64_t segment;
 };
 
 static int fill_linear(StreamLinear &L, const HostLinear &h, int y_dtype) {
@@ -944,7 +951,7 @@ static int fill_linear(StreamLinear &L, const HostLinear &h, int y_dtype) {
     L.x = h.x; L.absmax = h.absmax; L.absmax2 = h.absmax2; L.bias = h.bias; L.y = h.y; L.acc = h.acc;
     L.x_ld = h.x_ld;
     L.N = (int)h.N; L.K = (int)h.K; L.nb = (int)(Kp / 64); L.nbv = (int)((h.K + 63) / 64);
-    L.pad_ = 0;
+    L.segment = (int)h.segment;
     L.x_period = (int)(h.x_period > 0 ? h.x_period : h.K);
     L.y_dtype = y_dtype;
     L.x_vec_ok = (h.x_ld % 8 == 0) && (L.x_period % 8 == 0) && (h.K % 8 == 0) && aligned16(h.x);
@@ -953,7 +960,7 @@ static int fill_linear(StreamLinear &L, const HostLinear &h, int y_dtype) {
 }
 
 template <typename XT>
-static int launch_stream(StreamArgs &args, cudaStream_t st, bool pdl = false) {
+static int launch_stream(StreamArgs &args, cudaStream_t st, bool pdl = false, bool cooperative = false) {
     args.zero = 0u;
     args.sleep_cons = 32u; args.sleep_other = 200u;
     const int smem = SG_SMEM_BYTES;
@@ -970,9 +977,15 @@ static int launch_stream(StreamArgs &args, cudaStream_t st, bool pdl = false) {
     memset(&cfg, 0, sizeof(cfg));
     cfg.gridDim = dim3((unsigned)grid); cfg.blockDim = dim3(SG_THREADS); cfg.dynamicSmemBytes = (size_t)smem; cfg.stream = st;
     cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr; cfg.numAttrs = pdl ? 1 : 0;
+    if (cooperative) {
+        // CTAs of one launch wait for each other's closing steps: all of them have to be resident
+        attr[0].id = cudaLaunchAttributeCooperative;
+        attr[0].val.cooperative = 1;
+    } else {
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+    }
+    cfg.attrs = attr; cfg.numAttrs = (pdl || cooperative) ? 1 : 0;
     MPSBNB_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemv4_stream_kernel<XT>, args));
     return check_launch();
 }
@@ -1008,7 +1021,7 @@ int gemv4_stream_single(const void *x, int x_dtype, int64_t M, const uint8_t *pa
     StreamArgs args;
     memset(&args, 0, sizeof(args));
     args.lins = nullptr; args.units = nullptr;
-    HostLinear h{x, K, K, packed, absmax, absmax2, bias, y, nullptr, N, K};
+    HostLinear h{x, K, K, packed, absmax, absmax2, bias, y, nullptr, N, K, 0};
     int rc = fill_linear(args.one, h, y_dtype);
     if (rc != MPSBNB_OK) return rc;
     args.nunits = (int)((N + SG_ROWS - 1) / SG_ROWS);
@@ -1067,10 +1080,10 @@ extern "C" int mpsbnb_gemv_4bit_group_plan(const mpsbnb_linear4_desc *descs, int
     StreamLinear *lins = reinterpret_cast<StreamLinear *>(host);
     StreamUnit *units = reinterpret_cast<StreamUnit *>(host + lin_bytes);
     int rc = MPSBNB_OK;
-    int acc_parts = 0;
+    int acc_parts = 0, n_segments = 1;
     for (int i = 0; i < n_linears && rc == MPSBNB_OK; ++i) {
         HostLinear h{descs[i].x, descs[i].x_ld, descs[i].x_period, descs[i].packed, descs[i].absmax, descs[i].absmax2,
-                     descs[i].bias, descs[i].y, descs[i].acc, descs[i].N, descs[i].K};
+                     descs[i].bias, descs[i].y, descs[i].acc, descs[i].N, descs[i].K, descs[i].segment};
         rc = fill_linear(lins[i], h, y_dtype);
     }
     if (rc == MPSBNB_OK) {
@@ -1078,11 +1091,24 @@ extern "C" int mpsbnb_gemv_4bit_group_plan(const mpsbnb_linear4_desc *descs, int
         // the rest of the launch still runs), within each class longest first so that the round-robin
         // remainder consists of the short ones
         int nu2 = 0;
-        for (int i = 0; i < n_linears; ++i)
-            if (lins[i].acc != nullptr) acc_parts += ((lins[i].nb + SG_STAGE_BLOCKS - 1) / SG_STAGE_BLOCKS + chunk - 1) / chunk;
+        for (int i = 0; i < n_linears; ++i) {
+            if (lins[i].segment < 0 || lins[i].segment >= 0x7fff) rc = MPSBNB_ERR_INVALID_ARG;
+            else if (lins[i].segment + 1 > n_segments) n_segments = lins[i].segment + 1;
+        }
+        // contributions per accumulator tile: the same in every segment (the closing step counts to one number)
+        for (int seg = 0; seg < n_segments && rc == MPSBNB_OK; ++seg) {
+            int parts = 0;
+            for (int i = 0; i < n_linears; ++i)
+                if (lins[i].segment == seg && lins[i].acc != nullptr)
+                    parts += ((lins[i].nb + SG_STAGE_BLOCKS - 1) / SG_STAGE_BLOCKS + chunk - 1) / chunk;
+            if (seg == 0) acc_parts = parts;
+            else if (parts != acc_parts) rc = MPSBNB_ERR_UNSUPPORTED;
+        }
+        for (int seg = 0; seg < n_segments; ++seg)
         for (int cls = 0; cls < 2; ++cls)
         for (int pass = chunk * 8; pass >= 1; --pass) {
             for (int i = 0; i < n_linears; ++i) {
+                if (lins[i].segment != seg) continue;
                 if ((lins[i].acc != nullptr) != (cls == 0)) continue;
                 const int S = (lins[i].nb + SG_STAGE_BLOCKS - 1) / SG_STAGE_BLOCKS;
                 const int step = lins[i].acc != nullptr ? chunk : S;
@@ -1094,7 +1120,7 @@ extern "C" int mpsbnb_gemv_4bit_group_plan(const mpsbnb_linear4_desc *descs, int
                 }
             }
         }
-        if (nu2 != nu) rc = MPSBNB_ERR_INVALID_ARG;
+        if (rc == MPSBNB_OK && nu2 != nu) rc = MPSBNB_ERR_INVALID_ARG;
     }
     if (rc == MPSBNB_OK) {
         cudaStream_t st = (cudaStream_t)stream;
@@ -1118,6 +1144,7 @@ extern "C" int mpsbnb_gemv_4bit_group_plan(const mpsbnb_linear4_desc *descs, int
     plan_out->wait_flags = nullptr; plan_out->wait_step = nullptr;
     plan_out->wait_n = plan_out->wait_mul = plan_out->wait_add = 0;
     plan_out->acc_parts = acc_parts;
+    plan_out->n_segments = n_segments; plan_out->pad_ = 0;
     memset(&plan_out->ep, 0, sizeof(plan_out->ep));
     return MPSBNB_OK;
 }
@@ -1146,7 +1173,10 @@ extern "C" int mpsbnb_gemv_4bit_group_run(const mpsbnb_group_plan *plan, void *s
             return MPSBNB_ERR_INVALID_ARG;
         args.ep = e;
     }
-    const bool pdl = (plan->flags & MPSBNB_GROUP_PDL) != 0;
-    return plan->x_dtype == MPSBNB_F16 ? launch_stream<__half>(args, (cudaStream_t)stream, pdl)
-                                       : launch_stream<__nv_bfloat16>(args, (cudaStream_t)stream, pdl);
+    const bool coop = plan->n_segments > 1;
+    if (coop && (plan->ep.tile_cnt == nullptr || plan->wait_n <= 0 || plan->ep.peer_flags == nullptr))
+        return MPSBNB_ERR_INVALID_ARG;                             // later segments need the streamed closing step and its flags
+    const bool pdl = (plan->flags & MPSBNB_GROUP_PDL) != 0 && !coop;
+    return plan->x_dtype == MPSBNB_F16 ? launch_stream<__half>(args, (cudaStream_t)stream, pdl, coop)
+                                       : launch_stream<__nv_bfloat16>(args, (cudaStream_t)stream, pdl, coop);
 }

@@ -95,7 +95,7 @@ class LayerStack:
 
     def __init__(self, cfg: StackConfig, device, quant_type: str = "nf4", double_quant: bool = True,
                  layers: Optional[int] = None, rank: int = 0, world: int = 1, seed: int = 1000,
-                 dtype: torch.dtype = torch.float16, group=None, use_pdl: bool = True, fused_exchange: bool = True, boundary: Optional[str] = None):
+                 dtype: torch.dtype = torch.float16, group=None, use_pdl: bool = True, fused_exchange: bool = True, boundary: Optional[str] = None, persistent: bool = False):
         self.cfg, self.device, self.dtype = cfg, torch.device(device), dtype
         self.layers = cfg.layers if layers is None else layers
         self.rank, self.world, self.group = rank, world, group
@@ -114,8 +114,12 @@ class LayerStack:
         if boundary not in ("kernel", "inline", "stream"):
             raise ValueError("boundary must be 'kernel', 'inline' or 'stream'")
         self.boundary = boundary
+        # with the streamed boundary, ONE cooperative launch per step covers all layers (segment = layer): the
+        # weight stream never drains at a layer boundary
+        self.persistent = persistent and boundary == "stream"
         self.in_kernel_boundary = boundary != "kernel"
-        self._fused = False
+        self._fused = self._stream = self._persist = False
+        self._nbuf = 2
         self._peer_bases = []
         self.quant_type, self.double_quant = quant_type, double_quant
         self.alpha = cfg.alpha()
@@ -160,11 +164,14 @@ class LayerStack:
         self._fused = self.fused_exchange and M <= 8
         self._stream = self.boundary == "stream" and M <= 8 and (g == 1 or self._fused)
         self._nbuf = 3 if self._stream else 2
-        if self._fused:
+        self._persist = self.persistent and self._stream
+        if self._fused or self._persist:
             self._setup_exchange(M)
         elif self._stream:
             self.hbuf = torch.zeros(self._nbuf, M, cfg.hidden, dtype=dt, device=dev)
-        if M <= 8:
+        if self._persist:
+            self._build_persistent_plan(M)
+        elif M <= 8:
             self._build_plans(M)
 
     # ------------------------------------------------------------------ fused exchange (world > 1, batch <= 8)
@@ -182,13 +189,14 @@ class LayerStack:
         self.acks = self._xbuf[h_bytes + 256:h_bytes + 256 + 4 * g].view(torch.int32)
         self.step_ctr = torch.zeros(1, dtype=torch.int32, device=dev)
         self.h_out = torch.zeros(M, cfg.hidden, dtype=self.dtype, device=dev)
-        handle = (C.c_ubyte * 64)()
-        off = C.c_int64(0)
-        N.check(lib.mpsbnb_ipc_export(N.ptr(self._xbuf), handle, C.byref(off)), "ipc_export")
-        mine = (bytes(handle), int(off.value))
         everyone = [None] * g
-        torch.cuda.synchronize()
-        torch.distributed.all_gather_object(everyone, mine, group=self.group)
+        if g > 1:
+            handle = (C.c_ubyte * 64)()
+            off = C.c_int64(0)
+            N.check(lib.mpsbnb_ipc_export(N.ptr(self._xbuf), handle, C.byref(off)), "ipc_export")
+            mine = (bytes(handle), int(off.value))
+            torch.cuda.synchronize()
+            torch.distributed.all_gather_object(everyone, mine, group=self.group)
         bases = []
         for r in range(g):
             if r == self.rank:
@@ -203,8 +211,10 @@ class LayerStack:
         self._peer_h = [torch.tensor([b + p * one for b in bases], dtype=torch.int64, device=dev) for p in range(nb)]
         self._peer_flags = torch.tensor([b + h_bytes for b in bases], dtype=torch.int64, device=dev)
         self._peer_acks = torch.tensor([b + h_bytes + 256 for b in bases], dtype=torch.int64, device=dev)
+        self._peer_h_all = torch.cat(self._peer_h)                # [buffer][rank]
         torch.cuda.synchronize()
-        torch.distributed.barrier(group=self.group)              # every rank has mapped every buffer (all zero)
+        if g > 1:
+            torch.distributed.barrier(group=self.group)          # every rank has mapped every buffer (all zero)
 
     def _close_exchange(self):
         for b in self._peer_bases:
@@ -213,7 +223,7 @@ class LayerStack:
 
     def _x_of_layer(self, l: int) -> torch.Tensor:
         """Input h of layer l: the parity buffer in the fused exchange, else the one h."""
-        return self.hbuf[l % self._nbuf] if (self._fused or self._stream) else self.h
+        return self.hbuf[l % self._nbuf] if (self._fused or self._stream or self._persist) else self.h
 
     def _build_plans(self, M: int):
         """One grouped-launch plan per layer: q, k, v, gate, up store their outputs; o and down add
@@ -273,6 +283,48 @@ class LayerStack:
             self._plans.append(plan)
             self._plan_mem.append(mem)
 
+    def _build_persistent_plan(self, M: int):
+        """One plan for the whole stack: 7 L linears, segment = layer.  Layer l reads h from buffer l % 3; the closing
+        step of segment l (streamed, by tiles) writes buffer (l + 1) % 3 on every rank and raises the flags to
+        step * L + l + 1; linears of layer l wait for flags >= step * L + l."""
+        cfg, lib, g, L = self.cfg, N.lib(), self.world, self.layers
+        n = 7 * L
+        descs = (N.Linear4Desc * n)()
+        self.out_layers = []
+        for l in range(L):
+            outs = {name: torch.zeros(M, nn // g, dtype=self.dtype, device=self.device) for name, nn, _ in cfg.projections()}
+            self.out_layers.append(outs)
+            for i, pr in enumerate(self.proj[l]):
+                d = descs[7 * l + i]
+                d.x, d.x_ld = self.hbuf[l % self._nbuf].data_ptr(), cfg.hidden
+                d.x_period = cfg.hidden if pr.name == "down" else 0
+                d.packed, d.absmax = pr.packed.data_ptr(), pr.absmax.data_ptr()
+                d.absmax2 = None if pr.absmax2 is None else pr.absmax2.data_ptr()
+                d.bias = None
+                if pr.name in ("o", "down"):
+                    d.y, d.acc = None, self.acc.data_ptr()
+                else:
+                    d.y, d.acc = outs[pr.name].data_ptr(), None
+                d.N, d.K, d.segment = pr.n, pr.k, l
+        self.out = self.out_layers[-1]
+        nbytes = lib.mpsbnb_gemv_4bit_group_plan_bytes(descs, C.c_int(n))
+        self._plan_mem = [torch.empty(nbytes, dtype=torch.uint8, device=self.device)]
+        plan = N.GroupPlan()
+        N.check(lib.mpsbnb_gemv_4bit_group_plan(descs, C.c_int(n), N.i64(M), N.dt(self.dtype), N.dt(self.dtype),
+                                                C.c_int(N.qt(self.quant_type)), N.ptr(self._plan_mem[0]), C.c_size_t(nbytes),
+                                                C.byref(plan), N.stream()), "gemv_4bit_group_plan")
+        self._ep_counter = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self._tile_cnt = torch.zeros((cfg.hidden // g + 31) // 32, dtype=torch.int32, device=self.device)
+        ep = plan.ep
+        ep.acc, ep.alpha, ep.counter = self.acc.data_ptr(), self.alpha, self._ep_counter.data_ptr()
+        ep.M, ep.hs, ep.H, ep.rank, ep.nranks = M, cfg.hidden // g, cfg.hidden, self.rank, g
+        ep.peer_h, ep.nbuf, ep.peer_flags = self._peer_h_all.data_ptr(), self._nbuf, self._peer_flags.data_ptr()
+        ep.step, ep.mul, ep.add = self.step_ctr.data_ptr(), L, 1
+        ep.tile_cnt, ep.tile_expect = self._tile_cnt.data_ptr(), plan.acc_parts
+        plan.wait_flags, plan.wait_step = self.flags.data_ptr(), self.step_ctr.data_ptr()
+        plan.wait_n, plan.wait_mul, plan.wait_add = g, L, 0
+        self._plans = [plan]
+
     def _gemv(self, pr: _Proj, x: torch.Tensor, y: torch.Tensor, M: int):
         lib = N.lib()
         if M <= lib.mpsbnb_gemv_4bit_max_m():
@@ -289,6 +341,21 @@ class LayerStack:
     def _run_layers(self, M: int):
         """Enqueue one step (all layers) on the current stream."""
         cfg, lib, g = self.cfg, N.lib(), self.world
+        if self._persist:
+            L = self.layers
+            if g > 1:     # every rank has copied the previous step's result out of its h buffers
+                N.check(lib.mpsbnb_flags_wait(N.ptr(self.acks), C.c_int(g), N.ptr(self.step_ctr), C.c_int(1), C.c_int(0),
+                                              C.c_int(0), N.stream()), "flags_wait")
+            N.check(lib.mpsbnb_gemv_4bit_group_run(C.byref(self._plans[0]), N.stream()), "gemv_4bit_group_run")
+            if g > 1:     # ... and every rank's last shard has landed here
+                N.check(lib.mpsbnb_flags_wait(N.ptr(self.flags), C.c_int(g), N.ptr(self.step_ctr), C.c_int(L), C.c_int(L),
+                                              C.c_int(0), N.stream()), "flags_wait")
+            self.h_out.copy_(self.hbuf[L % self._nbuf])
+            N.check(lib.mpsbnb_counter_add(N.ptr(self.step_ctr), C.c_int(1), N.stream()), "counter_add")
+            if g > 1:
+                N.check(lib.mpsbnb_flags_push(N.ptr(self._peer_acks), C.c_int(self.rank), C.c_int(g), N.ptr(self.step_ctr),
+                                              C.c_int(1), C.c_int(0), N.stream()), "flags_push")
+            return
         if self._plans is not None and self._fused:
             hs, L = cfg.hidden // g, self.layers
             for l in range(L):
@@ -390,7 +457,7 @@ class LayerStack:
         return self._result()
 
     def _result(self) -> torch.Tensor:
-        if self._fused:
+        if self._fused or self._persist:
             return self.h_out
         return self.hbuf[self.layers % self._nbuf] if self._stream else self.h
 
@@ -400,6 +467,8 @@ class LayerStack:
 
     def launches_per_step(self) -> int:
         """Kernels of this library launched per step (NCCL's own kernels not counted)."""
+        if self._persist:
+            return 3 + (3 if self.world > 1 else 0)                  # input stage, the one GEMV launch, step counter (+ waits, acks)
         if self._plans is not None and self._fused:
             return 1 + self.layers * (1 if self.in_kernel_boundary else 2) + 3                          # + flags_wait, counter_add, flags_push (the copy is torch's)
         if self._plans is not None and self.world == 1 and self.in_kernel_boundary:

@@ -53,6 +53,21 @@ def test_small_stack_matches_oracle(M, boundary, qt, dq):
     assert_device_ok()
 
 
+@pytest.mark.parametrize("M", [1, 5])
+def test_streamed_boundary_one_launch_per_layer(M):
+    """The streamed boundary without the whole-stack launch (persistent=False): one grouped launch per layer."""
+    cfg = S.StackConfig("tiny", hidden=256, ffn=704, kv=64, layers=4)
+    st = S.LayerStack(cfg, device="cuda:0", seed=6, boundary="stream", persistent=False)
+    x = np.random.default_rng(M).standard_normal((M, cfg.hidden)).astype(np.float16)
+    st.prepare(M, use_graph=True)
+    ref_h, _ = oracle_stack(st, x)
+    for _ in range(2):
+        h = st.step(torch.from_numpy(x).cuda())
+        torch.cuda.synchronize()
+        assert rel_err(to_np(h), ref_h) <= 1e-2
+    assert_device_ok()
+
+
 def test_llama7b_layer_shapes_one_layer():
     """One layer at the real Llama-2-7B widths, batch 1 (the benchmark's unit of work)."""
     st = S.LayerStack(S.LLAMA2_7B, device="cuda:0", layers=1, seed=9)
