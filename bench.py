@@ -216,7 +216,7 @@ def run_gpu(args, cfg):
     peaks = load_peaks()
     M = args.batch
     stack = S.LayerStack(cfg, device=f"cuda:{local}", rank=rank, world=world, layers=args.layers,
-                         fused_exchange=args.exchange == "fused", boundary=args.boundary, persistent=args.one_launch and not args.per_layer)
+                         fused_exchange=args.exchange == "fused", boundary=args.boundary, persistent=not args.per_layer)
     stack.prepare(M, use_graph=True)
     gen = torch.Generator(device="cpu"); gen.manual_seed(1)
     x_host = torch.randn(M, cfg.hidden, generator=gen).half().pin_memory()
@@ -329,7 +329,6 @@ def main():
                     help="layer boundary: its own small kernel, the closing step of the GEMV launch, or streamed tile "
                          "by tile from inside the launch (default)")
     ap.add_argument("--per-layer", action="store_true", help="one GEMV launch per layer instead of one per step")
-    ap.add_argument("--one-launch", action="store_true", help="one cooperative GEMV launch per step (all layers)")
     args = ap.parse_args()
     from mps_bitsandbytes_b200 import stack as S
     cfg = S.LLAMA2_7B if args.model == "llama2-7b" else S.LLAMA_70B

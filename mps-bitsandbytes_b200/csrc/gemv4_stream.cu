@@ -471,7 +471,6 @@ __global__ void __launch_bounds__(SG_THREADS, 1) gemv4_stream_kernel(const __gri
             const StreamLinear *L = lin_of(un.lin);
             const int buf = uc & 1;
             if (!mbar_wait_sleep(red_full(buf), (uint32_t)(uc >> 1) & 1u, abort_flag, a.sleep_other)) { atomicExch(&g_stream_status, 204); *abort_flag = 1; break; }
-            resolve_pending();                                   // the count issued one unit ago has long returned
             const float *red = reinterpret_cast<const float *>(p_generic0 + s_red + buf * SG_RED_BYTES);
             const int n = un.row0 + lane;
             for (int m = 0; m < a.M; ++m) {
@@ -496,13 +495,14 @@ __global__ void __launch_bounds__(SG_THREADS, 1) gemv4_stream_kernel(const __gri
             __syncwarp();
             if (lane == 0) mbar_arrive(red_empty(buf));
             if (a.ep.tile_cnt != nullptr && L->acc == a.ep.acc && L->acc != nullptr) {
-                // streamed closing step: count this unit's contribution to its 32-row tile.  The count is a release
-                // (it orders this warp's accumulator updates before it) and its result is looked at one unit
-                // later, so the round trip never stalls this warp.
+                // streamed closing step: count this unit's contribution to its 32-row tile.  The count is a release:
+                // it orders this warp's accumulator updates before it.
                 __syncwarp();
                 pend_tile = (L->segment << 16) | (un.row0 / SG_ROWS);
                 if (lane == 0)
                     asm volatile("atom.add.release.gpu.global.s32 %0, [%1], 1;" : "=r"(pend_old) : "l"(a.ep.tile_cnt + un.row0 / SG_ROWS) : "memory");
+                // looked at right away: the next unit may belong to a segment that cannot start before this tile is closed
+                resolve_pending();
             }
         }
         resolve_pending();

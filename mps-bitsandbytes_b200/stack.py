@@ -95,7 +95,7 @@ class LayerStack:
 
     def __init__(self, cfg: StackConfig, device, quant_type: str = "nf4", double_quant: bool = True,
                  layers: Optional[int] = None, rank: int = 0, world: int = 1, seed: int = 1000,
-                 dtype: torch.dtype = torch.float16, group=None, use_pdl: bool = True, fused_exchange: bool = True, boundary: Optional[str] = None, persistent: bool = False):
+                 dtype: torch.dtype = torch.float16, group=None, use_pdl: bool = True, fused_exchange: bool = True, boundary: Optional[str] = None, persistent: bool = True):
         self.cfg, self.device, self.dtype = cfg, torch.device(device), dtype
         self.layers = cfg.layers if layers is None else layers
         self.rank, self.world, self.group = rank, world, group

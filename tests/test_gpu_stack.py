@@ -68,6 +68,25 @@ def test_streamed_boundary_one_launch_per_layer(M):
     assert_device_ok()
 
 
+@pytest.mark.parametrize("M", [1, 3, 8])
+@pytest.mark.parametrize("qt,dq", [("nf4", True), ("fp4", False)])
+def test_whole_stack_in_one_launch(M, qt, dq):
+    """persistent=True: all layers in ONE cooperative launch (segment = layer); layers hand h over through flags."""
+    cfg = S.StackConfig("tiny", hidden=256, ffn=704, kv=64, layers=5)
+    st = S.LayerStack(cfg, device="cuda:0", quant_type=qt, double_quant=dq, seed=8, boundary="stream", persistent=True)
+    x = np.random.default_rng(10 + M).standard_normal((M, cfg.hidden)).astype(np.float16)
+    for use_graph in (False, True):
+        st.prepare(M, use_graph=use_graph)
+        ref_h, ref_out = oracle_stack(st, x)
+        for _ in range(3):
+            h = st.step(torch.from_numpy(x).cuda())
+            torch.cuda.synchronize()
+            assert rel_err(to_np(h), ref_h) <= 1e-2, use_graph
+            for name in ("q", "k", "v", "gate", "up"):
+                assert rel_err(to_np(st.out[name]), ref_out[name]) <= 1e-2, name
+    assert_device_ok()
+
+
 def test_llama7b_layer_shapes_one_layer():
     """One layer at the real Llama-2-7B widths, batch 1 (the benchmark's unit of work)."""
     st = S.LayerStack(S.LLAMA2_7B, device="cuda:0", layers=1, seed=9)
