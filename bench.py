@@ -6,9 +6,11 @@
 Workload (N = 1): the Llama-2-7B-shaped NF4 decode stack of BASELINE config 3 — 32 layers x
 {q,k,v,o 4096x4096, gate/up 11008x4096, down 4096x11008}, double-quantised absmax, fp16,
 batch 1 — one "step" = one pass over all 224 linears (3.34 GB of packed weights and absmax,
-far larger than the 126 MB L2, so every step streams from HBM).  For N > 1 (launched by
-torchrun, one rank per GPU) the stack is N-sharded over the ranks with an NCCL all-gather at
-each layer boundary; the per-GPU work shrinks with N (strong scaling of a fixed model).
+far larger than the 126 MB L2, so every step streams from HBM), by default ONE cooperative
+kernel launch.  For N > 1 (launched by torchrun, one rank per GPU) the stack is N-sharded over
+the ranks; at each layer boundary every rank stores its shard of the next input into all ranks'
+buffers over NVLink and raises flags (--exchange nccl: an NCCL all-gather instead); the per-GPU
+work shrinks with N (strong scaling of a fixed model).
 
 Prints ONE JSON line: metric nf4_decode_gbs = algorithmic bytes per step / step time, with
 the HBM roofline, an end-to-end figure through the public LayerStack API with host buffers,
@@ -286,7 +288,7 @@ def run_gpu(args, cfg):
                          "kernel": kname, "launches_per_step": n_gemv,
                          "bytes_per_launch": nbytes / world / n_gemv,
                          "note": "achieved = algorithmic bytes of the step / CUDA-event time of the whole step "
-                                 "(the GEMV launches plus one small boundary kernel per layer), per GPU"},
+                                 "(the GEMV launch(es) plus the small input / boundary / counter kernels), per GPU"},
             "e2e": {"value": e2e_gbs, "unit": "GB/s", "ms_per_step": e2e_ms, "h2d_bytes_per_step": x_host.numel() * 2,
                     "d2h_bytes_per_step": y_host.numel() * 2},
             "gpu_launches": stack.launches_per_step() * args.steps,
