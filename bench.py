@@ -43,7 +43,8 @@ sys.path.insert(0, ROOT)
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum of ONE gemv4_stream_kernel launch (one Llama-2-7B layer, batch 1,
-# whole layer on one GPU), from the ncu capture summarised in profiles/gemv4_stream_kernel_llama7b_layer.md
+# whole layer on one GPU), from the ncu capture summarised in profiles/gemv4_stream_kernel_llama7b_one_layer_per_launch.md;
+# a launch that covers all layers moves layers x this (the two-layer one-launch capture reads 213.5 MB for 2 layers)
 NCU_TRAFFIC_7B_LAYER_BYTES = 108.5e6
 
 
