@@ -219,7 +219,7 @@ def run_gpu(args, cfg):
     peaks = load_peaks()
     M = args.batch
     stack = S.LayerStack(cfg, device=f"cuda:{local}", rank=rank, world=world, layers=args.layers,
-                         fused_exchange=args.exchange == "fused", boundary=args.boundary, persistent=not args.per_layer)
+                         fused_exchange=args.exchange == "fused", boundary=args.boundary, persistent=not args.per_layer, mid_batch_tcgen05=not args.no_mid_tc)
     stack.prepare(M, use_graph=True)
     gen = torch.Generator(device="cpu"); gen.manual_seed(1)
     x_host = torch.randn(M, cfg.hidden, generator=gen).half().pin_memory()
@@ -332,6 +332,7 @@ def main():
                     help="layer boundary: its own small kernel, the closing step of the GEMV launch, or streamed tile "
                          "by tile from inside the launch (default)")
     ap.add_argument("--per-layer", action="store_true", help="one GEMV launch per layer instead of one per step")
+    ap.add_argument("--no-mid-tc", action="store_true", help="batch 9..16: per-linear launches of the older kernel instead of tcgen05")
     args = ap.parse_args()
     from mps_bitsandbytes_b200 import stack as S
     cfg = S.LLAMA2_7B if args.model == "llama2-7b" else S.LLAMA_70B

@@ -49,7 +49,7 @@ constexpr int TG_XS_BYTES = TG_X_BYTES + TG_A_BYTES;
 constexpr int TG_NXS = 4;                                  // scale/x slots (a multiple of TG_LOADERS: one loader per slot)
 constexpr int TG_MAX_SLOTS = 9;
 constexpr int TG_ABUFS = 3;                                // A tiles in tensor memory (128 columns each)
-constexpr int TG_MAX_M = 8;
+constexpr int TG_MAX_M = 16;                               // batch rows: the UMMA N
 constexpr uint32_t TG_LUT_ABS = 131072u;                   // table at an absolute shared address: see expander
 constexpr uint32_t TG_HIGH_ABS = TG_LUT_ABS + 65536u;      // entry b of lane l sits at b * 256 + l * 4: a 64 KiB span
 constexpr int TG_SMEM_BYTES = 227 * 1024;
@@ -281,8 +281,15 @@ __global__ void __launch_bounds__(TG_THREADS, 1) gemv4_tc_kernel(const __grid_co
             const int d = dcount & 1;
             if (!mbar_wait_sleep(dfull_bar(d), ((uint32_t)dcount >> 1) & 1u, abort_flag, kSleepSlow)) { atomicExch(&g_tc_status, 405); *abort_flag = 1; break; }
             tc_fence_after();
-            uint32_t v[8];
-            tmem_ld_32x8(tmem_base + ((uint32_t)(32 * e) << 16) + TG_D_COL0 + (uint32_t)(TG_N * d), v);
+            uint32_t v[16];
+            {
+                uint32_t lo[8], hi[8];
+                const uint32_t taddr = tmem_base + ((uint32_t)(32 * e) << 16) + TG_D_COL0 + (uint32_t)(TG_N * d);
+                tmem_ld_32x8(taddr, lo);
+                if (a.M > 8) tmem_ld_32x8(taddr + 8u, hi);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) { v[i] = lo[i]; v[8 + i] = a.M > 8 ? hi[i] : 0u; }
+            }
             tmem_ld_wait();
             tc_fence_before();
             __syncwarp();
@@ -298,13 +305,16 @@ __global__ void __launch_bounds__(TG_THREADS, 1) gemv4_tc_kernel(const __grid_co
             };
             if (acc != nullptr) {
                 if (mine)
-                    for (int m = 0; m < a.M; ++m) atomicAdd(acc + (int64_t)m * LN + n, __uint_as_float(v[m]) + (pc.s_begin == 0 ? bv : 0.0f));
+#pragma unroll
+                    for (int m = 0; m < TG_MAX_M; ++m) if (m < a.M) atomicAdd(acc + (int64_t)m * LN + n, __uint_as_float(v[m]) + (pc.s_begin == 0 ? bv : 0.0f));
             } else if (pc.parts == 1) {
                 if (mine)
-                    for (int m = 0; m < a.M; ++m) store_y(m, __uint_as_float(v[m]) + bv);
+#pragma unroll
+                    for (int m = 0; m < TG_MAX_M; ++m) if (m < a.M) store_y(m, __uint_as_float(v[m]) + bv);
             } else {
                 if (mine)
-                    for (int m = 0; m < a.M; ++m) atomicAdd(ws + (int64_t)m * LN + n, __uint_as_float(v[m]));
+#pragma unroll
+                    for (int m = 0; m < TG_MAX_M; ++m) if (m < a.M) atomicAdd(ws + (int64_t)m * LN + n, __uint_as_float(v[m]));
                 __threadfence();
                 __syncwarp();
                 int old = 0;
@@ -448,9 +458,10 @@ __global__ void __launch_bounds__(TG_THREADS, 1) gemv4_tc_kernel(const __grid_co
                               make_uint4(__float_as_uint(cur[4 * i]), __float_as_uint(cur[4 * i + 1]), __float_as_uint(cur[4 * i + 2]), __float_as_uint(cur[4 * i + 3])));
                 if (lane == 0) tg_sts32(s_mode + 4u * my_x, 0u);
             }
-            // x tile: row m of atom (lane >> 3), 16-byte chunk (lane & 7) ^ m  (128-byte swizzle)
+            // x tile: row m of atom (lane >> 3) (rows 8..15 are the second 8-row group, 1 KiB further), 16-byte chunk
+            // (lane & 7) ^ (m & 7)  (128-byte swizzle)
             for (int m = 0; m < a.M; ++m) {
-                const uint32_t dst = xb + (uint32_t)((lane >> 3) * 2048 + m * 128 + (((lane & 7) ^ m) << 4));
+                const uint32_t dst = xb + (uint32_t)((lane >> 3) * 2048 + (m >> 3) * 1024 + (m & 7) * 128 + (((lane & 7) ^ (m & 7)) << 4));
                 if (my_L->x_vec_ok) {
                     const int k0 = my_s * TG_STAGE_K + lane * 8;
                     const bool in = k0 < my_L->K;

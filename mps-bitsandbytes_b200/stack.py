@@ -95,7 +95,7 @@ class LayerStack:
 
     def __init__(self, cfg: StackConfig, device, quant_type: str = "nf4", double_quant: bool = True,
                  layers: Optional[int] = None, rank: int = 0, world: int = 1, seed: int = 1000,
-                 dtype: torch.dtype = torch.float16, group=None, use_pdl: bool = True, fused_exchange: bool = True, boundary: Optional[str] = None, persistent: bool = True):
+                 dtype: torch.dtype = torch.float16, group=None, use_pdl: bool = True, fused_exchange: bool = True, boundary: Optional[str] = None, persistent: bool = True, mid_batch_tcgen05: bool = True):
         self.cfg, self.device, self.dtype = cfg, torch.device(device), dtype
         self.layers = cfg.layers if layers is None else layers
         self.rank, self.world, self.group = rank, world, group
@@ -114,11 +114,12 @@ class LayerStack:
         if boundary not in ("kernel", "inline", "stream"):
             raise ValueError("boundary must be 'kernel', 'inline' or 'stream'")
         self.boundary = boundary
+        self.mid_batch_tcgen05 = mid_batch_tcgen05
         # with the streamed boundary, ONE cooperative launch per step covers all layers (segment = layer): the
         # weight stream never drains at a layer boundary
         self.persistent = persistent and boundary == "stream"
         self.in_kernel_boundary = boundary != "kernel"
-        self._fused = self._stream = self._persist = False
+        self._fused = self._stream = self._persist = self._inline = False
         self._nbuf = 2
         self._peer_bases = []
         self.quant_type, self.double_quant = quant_type, double_quant
@@ -165,6 +166,7 @@ class LayerStack:
         self._stream = self.boundary == "stream" and M <= 8 and (g == 1 or self._fused)
         self._nbuf = 3 if self._stream else 2
         self._persist = self.persistent and self._stream
+        self._inline = self.in_kernel_boundary and M <= 8         # closing step inside the GEMV launch (default kernel only)
         if self._fused or self._persist:
             self._setup_exchange(M)
         elif self._stream:
@@ -173,6 +175,15 @@ class LayerStack:
             self._build_persistent_plan(M)
         elif M <= 8:
             self._build_plans(M)
+        elif M <= 16 and self.mid_batch_tcgen05:
+            # batch 9 .. 16: grouped launches of the tcgen05 decode kernel (its MMAs are N = 16 wide anyway), one per
+            # layer, with the boundary as its own kernel
+            lib = N.lib()
+            old = lib.mpsbnb_decode_kernel_select(C.c_int(1))
+            try:
+                self._build_plans(M)
+            finally:
+                lib.mpsbnb_decode_kernel_select(C.c_int(old))
 
     # ------------------------------------------------------------------ fused exchange (world > 1, batch <= 8)
     def _setup_exchange(self, M: int):
@@ -259,7 +270,7 @@ class LayerStack:
                                                     C.c_int(N.qt(self.quant_type)), N.ptr(mem), C.c_size_t(nbytes),
                                                     C.byref(plan), N.stream()), "gemv_4bit_group_plan")
             plan.flags = N.GROUP_PDL if (self.use_pdl or self._fused) else 0
-            if self.in_kernel_boundary and (g == 1 or self._fused):
+            if self._inline and (g == 1 or self._fused):
                 # the CTA that finishes last writes alpha * (o + down) as the next layer's h (into every rank's
                 # buffer when fused) and re-arms the accumulator: no boundary kernel
                 ep = plan.ep
@@ -360,7 +371,7 @@ class LayerStack:
             hs, L = cfg.hidden // g, self.layers
             for l in range(L):
                 N.check(lib.mpsbnb_gemv_4bit_group_run(C.byref(self._plans[l]), N.stream()), "gemv_4bit_group_run")
-                if self.in_kernel_boundary:
+                if self._inline:
                     continue
                 N.check(lib.mpsbnb_stack_boundary_push(N.ptr(self.acc), C.c_float(self.alpha), N.i64(M), N.i64(hs),
                                                        N.i64(cfg.hidden), C.c_int(self.rank), C.c_int(g),
@@ -380,7 +391,7 @@ class LayerStack:
             hs = cfg.hidden // g
             for l in range(self.layers):
                 N.check(lib.mpsbnb_gemv_4bit_group_run(C.byref(self._plans[l]), N.stream()), "gemv_4bit_group_run")
-                if self.in_kernel_boundary and g == 1:
+                if self._inline and g == 1:
                     continue
                 dst = self.h if g == 1 else self.h_shard
                 N.check(lib.mpsbnb_stack_boundary_acc(N.ptr(self.acc), C.c_float(self.alpha), N.i64(M * hs), N.ptr(dst),
@@ -470,8 +481,8 @@ class LayerStack:
         if self._persist:
             return 3 + (3 if self.world > 1 else 0)                  # input stage, the one GEMV launch, step counter (+ waits, acks)
         if self._plans is not None and self._fused:
-            return 1 + self.layers * (1 if self.in_kernel_boundary else 2) + 3                          # + flags_wait, counter_add, flags_push (the copy is torch's)
-        if self._plans is not None and self.world == 1 and self.in_kernel_boundary:
+            return 1 + self.layers * (1 if self._inline else 2) + 3                          # + flags_wait, counter_add, flags_push (the copy is torch's)
+        if self._plans is not None and self.world == 1 and self._inline:
             return 1 + self.layers
         if self._plans is not None:
             return 1 + self.layers * (2 if self.world == 1 else 3)

@@ -29,7 +29,7 @@ def oracle_stack(st: S.LayerStack, x: np.ndarray):
 
 
 @pytest.mark.parametrize("M,boundary", [(1, "kernel"), (1, "inline"), (1, "stream"), (3, "inline"), (3, "stream"),
-                                        (8, "kernel"), (8, "stream"), (16, "kernel")])
+                                        (8, "kernel"), (8, "stream"), (12, "kernel"), (16, "kernel"), (24, "kernel")])
 @pytest.mark.parametrize("qt,dq", [("nf4", True), ("fp4", False)])
 def test_small_stack_matches_oracle(M, boundary, qt, dq):
     """boundary: the layer boundary as its own kernel, as the closing step of the grouped GEMV launch (last CTA), or
