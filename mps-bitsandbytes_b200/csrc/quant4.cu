@@ -90,48 +90,72 @@ quantize4_fast_kernel(const T *__restrict__ A, int64_t rows, int64_t cols, int64
                       const float *__restrict__ absmax_in, uint8_t *__restrict__ packed,
                       float *__restrict__ absmax_out) {
     static_assert(sizeof(T) == 2, "fast path takes 16-bit input");
+    constexpr int U = 4;                                   // 16-byte loads in flight per thread: the kernel is a
+                                                           // pure stream and needs ~100 KB in flight per SM
     const int64_t total = rows * chunks_per_row;           // multiple of LPB
     const int64_t nwarp_iters = (total + 31) / 32;
     const int lane = threadIdx.x & 31;
     const int64_t warp0 = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const int64_t nwarps = (int64_t)gridDim.x * (blockDim.x >> 5);
-    for (int64_t wi = warp0; wi < nwarp_iters; wi += nwarps) {
-        const int64_t c = wi * 32 + lane;
-        const bool live = c < total;
-        const int64_t row = live ? c / chunks_per_row : 0;
-        const int64_t kc = live ? c - row * chunks_per_row : 0;
-        const int64_t k0 = kc * 8;
-        uint4 raw = make_uint4(0u, 0u, 0u, 0u);            // zero padding beyond K
-        if (live && k0 < cols) raw = __ldg(reinterpret_cast<const uint4 *>(A + row * cols + k0));
-        float x[8];
-        {
-            const T *h = reinterpret_cast<const T *>(&raw);
+    const bool small = total < 0x7fffffffll && chunks_per_row < 0x7fffffffll;   // 32-bit index arithmetic
+    for (int64_t wb = warp0; wb < nwarp_iters; wb += nwarps * U) {
+        uint4 raw[U];
+        int64_t cs[U], rowv[U], kcv[U];
+        bool livev[U];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) x[j] = to_f32<T>(h[j]);
+        for (int u = 0; u < U; ++u) {
+            const int64_t wi = wb + (int64_t)u * nwarps;
+            const int64_t c = wi * 32 + lane;
+            const bool live = wi < nwarp_iters && c < total;
+            int64_t row, kc;
+            if (small) {
+                const uint32_t c32 = live ? (uint32_t)c : 0u, cpr = (uint32_t)chunks_per_row;
+                const uint32_t r32 = c32 / cpr;
+                row = r32; kc = c32 - r32 * cpr;
+            } else {
+                row = live ? c / chunks_per_row : 0;
+                kc = live ? c - row * chunks_per_row : 0;
+            }
+            cs[u] = c; rowv[u] = row; kcv[u] = kc; livev[u] = live;
+            raw[u] = make_uint4(0u, 0u, 0u, 0u);           // zero padding beyond K
+            if (live && kc * 8 < cols) raw[u] = __ldg(reinterpret_cast<const uint4 *>(A + row * cols + kc * 8));
         }
-        const int64_t blk = row * (chunks_per_row / LPB) + kc / LPB;
-        float a;
-        if (absmax_in != nullptr) {
-            a = live ? absmax_in[blk] : 1.0f;
-        } else {
-            a = 0.0f;
 #pragma unroll
-            for (int j = 0; j < 8; ++j) a = fmaxf(a, fabsf(x[j]));
+        for (int u = 0; u < U; ++u) {
+            // warp-uniform: the shuffles below need the whole warp
+            if (wb + (int64_t)u * nwarps >= nwarp_iters) break;
+            const bool live = livev[u];
+            const int64_t row = rowv[u], kc = kcv[u];
+            float x[8];
+            {
+                const T *h = reinterpret_cast<const T *>(&raw[u]);
 #pragma unroll
-            for (int o = 1; o < LPB; o <<= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
-            a = fmaxf(a, 1e-8f);                           // clamp(min=1e-8)
-            if (live && (lane & (LPB - 1)) == 0) absmax_out[blk] = a;
+                for (int j = 0; j < 8; ++j) x[j] = to_f32<T>(h[j]);
+            }
+            const int64_t blk = row * (chunks_per_row / LPB) + kc / LPB;
+            float a;
+            if (absmax_in != nullptr) {
+                a = live ? absmax_in[blk] : 1.0f;
+            } else {
+                a = 0.0f;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) a = fmaxf(a, fabsf(x[j]));
+#pragma unroll
+                for (int o = 1; o < LPB; o <<= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
+                a = fmaxf(a, 1e-8f);                           // clamp(min=1e-8)
+                if (live && (lane & (LPB - 1)) == 0) absmax_out[blk] = a;
+            }
+            uint32_t word = 0;
+            if (a >= 1e-30f && a <= 1e30f && absmax_in == nullptr) {   // range covered by the proof
+                const float r = __frcp_rn(a);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) word |= code_of<QT>(block_div<true>(x[j], a, r)) << (4 * j);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) word |= code_of<QT>(block_div<false>(x[j], a, 0.f)) << (4 * j);
+            }
+            if (live) reinterpret_cast<uint32_t *>(packed)[cs[u]] = word;   // byte j/2: low nibble = even k
         }
-        uint32_t word = 0;
-        if (a >= 1e-30f && a <= 1e30f && absmax_in == nullptr) {   // range covered by the proof
-            const float r = __frcp_rn(a);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) word |= code_of<QT>(block_div<true>(x[j], a, r)) << (4 * j);
-        } else {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) word |= code_of<QT>(block_div<false>(x[j], a, 0.f)) << (4 * j);
-        }
-        if (live) reinterpret_cast<uint32_t *>(packed)[c] = word;   // byte j/2: low nibble = even k
     }
 }
 
