@@ -331,6 +331,50 @@ int mpsbnb_linear_int8(const void *x, int x_dtype, int64_t M, const int8_t *W,
                        const void *bias, void *y, int y_dtype, void *workspace,
                        size_t workspace_bytes, void *stream);
 
+/* nn/outlier_aware.py:84-146 OutlierAwareLinear.forward (LLM.int8 mixed-precision decomposition):
+ *   y = deq(quantize_rowwise(x_main)) . deq(W_main)^T + x_outlier . outlier_w^T + bias
+ * with x_main / W_main the columns NOT listed in outlier_idx, both dequantised as
+ * q.to(op) * (scale / 127).to(op) (:118-119, :138-139).  The reference has no native binding for
+ * it (three Python matmuls); here the re-quantised x, the dequantised W and the 16-bit outlier
+ * columns form the two operands of ONE tcgen05 GEMM over the full K.
+ *   x           [M, K] in x_dtype (F16, BF16 or F32)
+ *   W, w_scales int8 [N, K] (entries in outlier columns are ignored), fp32 [N] row maxima
+ *   outlier_idx int64 [n_outliers] distinct column numbers (may be NULL when n_outliers == 0:
+ *               the pure INT8 path, :112-121); outlier_w [N, n_outliers] in op_dtype
+ *   bias        NULL or [N] in op_dtype; op_dtype F16 or BF16 (the module's compute_dtype)
+ *   y           [M, N] in y_dtype
+ * workspace: mpsbnb_outlier_linear_workspace_bytes(M, N, K) bytes, 256-byte aligned. */
+size_t mpsbnb_outlier_linear_workspace_bytes(int64_t M, int64_t N, int64_t K);
+int mpsbnb_outlier_linear(const void *x, int x_dtype, int64_t M, const int8_t *W, const float *w_scales,
+                          const int64_t *outlier_idx, int64_t n_outliers, const void *outlier_w,
+                          int64_t N, int64_t K, const void *bias, int op_dtype, void *y, int y_dtype,
+                          void *workspace, size_t workspace_bytes, void *stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Quantised embedding look-ups (gather + dequantise in one pass)
+ * ------------------------------------------------------------------------------------- */
+
+/* nn/embedding.py:78-139 Embedding4bit.forward; bindings replaced: _C.embedding_4bit_nf4 /
+ * _C.embedding_4bit_fp4 (:94-101).  out[t, :] = code[nibble] * absmax[row, k / blocksize] for
+ * row = indices[t], computed in fp32 and rounded once (functional.py:388-416 on one row).
+ *   indices   int32 (index_bytes 4) or int64 (index_bytes 8) [n_indices]
+ *   packed    uint8 [num_embeddings, packed_ld] (packed_ld >= dim / 2 bytes per row; dim even)
+ *   absmax    fp32 [num_embeddings, ceil(dim / blocksize)]
+ *   padding_idx  rows with this index give zeros (:135-137); negative = none
+ *   out       [n_indices, dim] in out_dtype
+ * An index outside [0, num_embeddings) gives a zero row (the kernel neither faults nor raises;
+ * the Python path of the reference raises IndexError). */
+int mpsbnb_embedding_4bit(const void *indices, int index_bytes, int64_t n_indices, const uint8_t *packed,
+                          int64_t packed_ld, const float *absmax, int64_t num_embeddings, int64_t dim,
+                          int blocksize, int quant_type, int64_t padding_idx, void *out, int out_dtype,
+                          void *stream);
+/* nn/embedding.py:244-275 Embedding8bit.forward; binding replaced: _C.embedding_8bit (:252-256).
+ * out[t, k] = T(q[row, k]) * T(scales[row] / 127), the scale rounded to out_dtype first (:269).
+ *   q int8 [num_embeddings, dim], scales fp32 [num_embeddings]; other arguments as above. */
+int mpsbnb_embedding_8bit(const void *indices, int index_bytes, int64_t n_indices, const int8_t *q,
+                          const float *scales, int64_t num_embeddings, int64_t dim, int64_t padding_idx,
+                          void *out, int out_dtype, void *stream);
+
 /* ---------------------------------------------------------------------------------------
  * FP8 E4M3 (row-scaled)
  * ------------------------------------------------------------------------------------- */

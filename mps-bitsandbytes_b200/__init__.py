@@ -14,7 +14,11 @@ from .functional import (  # noqa: F401
     dequantize_nf4, dequantize_rowwise, double_quant, matmul_4bit, matmul_colrow, matmul_fp4,
     matmul_fp8_e4m3, matmul_int8, matmul_nf4, quantize_4bit, quantize_blockwise, quantize_colrow,
     quantize_fp4, quantize_fp8_e4m3, quantize_nf4, quantize_rowwise)
-from .nn import Linear4bit, Linear8bit, LinearFP8, Params4bit  # noqa: F401
+from .nn import (  # noqa: F401
+    Embedding4bit, Embedding8bit, EmbeddingFP4, EmbeddingNF4, Linear4bit, Linear8bit, LinearFP8,
+    OutlierAwareLinear, Params4bit)
+from .integration import (  # noqa: F401
+    BitsAndBytesConfig, get_memory_footprint, quantize_model, replace_linear_with_4bit, replace_linear_with_8bit)
 
 
 def is_available() -> bool:

@@ -64,7 +64,8 @@ def lib():
         l.mpsbnb_status_string.restype = C.c_char_p
         l.mpsbnb_last_cuda_error_string.restype = C.c_char_p
         for name in ("mpsbnb_gemv_4bit_group_plan_bytes", "mpsbnb_gemm_4bit_workspace_bytes", "mpsbnb_matmul_int8_workspace_bytes",
-                     "mpsbnb_linear_int8_workspace_bytes", "mpsbnb_linear_fp8_workspace_bytes"):
+                     "mpsbnb_linear_int8_workspace_bytes", "mpsbnb_linear_fp8_workspace_bytes",
+                     "mpsbnb_outlier_linear_workspace_bytes", "mpsbnb_gemm_4bit_static_max_bytes", "mpsbnb_gemm_4bit_static_bytes"):
             if hasattr(l, name):
                 getattr(l, name).restype = C.c_size_t
         _lib = l

@@ -63,6 +63,37 @@ template <> __device__ __forceinline__ __half from_f32<__half>(float v) { return
 template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
 template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
 
+// ------------------------------------------------------------------ int8 helpers shared by the 8-bit kernels
+// `127.0 / scale` as torch evaluates it for a Python scalar over a tensor: reciprocal, then times 127
+// (two roundings; decides round-half-even ties, mps_bitsandbytes/functional.py:518, 621, 852, 859, 920).
+__device__ __forceinline__ float rdiv127(float s) { return __fmul_rn(__frcp_rn(s), 127.0f); }
+
+__device__ __forceinline__ int8_t quant_i8(float x, float f) {
+    float v = rintf(__fmul_rn(x, f));                       // torch.round: half to even
+    return (int8_t)(int)fminf(fmaxf(v, -127.0f), 127.0f);
+}
+
+// CTA-wide max of non-negative values; every thread gets the result.
+__device__ __forceinline__ float cta_max(float a, float *red) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
+    __syncthreads();                                        // red[] may still be read by a previous use
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = a;
+    __syncthreads();
+    a = red[0];
+    for (int w = 1; w < (int)(blockDim.x >> 5); ++w) a = fmaxf(a, red[w]);
+    return a;
+}
+
+// q (exact in T) times a scale that is rounded to T FIRST, the product rounded to T: the form
+// `q.to(dtype) * (scales / 127.0).to(dtype)` of mps_bitsandbytes/nn/embedding.py:269 and
+// nn/outlier_aware.py:118-119.  The product of two 16-bit floats is exact in fp32, so one fp32 multiply and
+// one rounding equal the multiply in T.
+template <typename T> __device__ __forceinline__ T i8_times_rounded_scale(int8_t q, float s_over_127) {
+    const float s = to_f32<T>(from_f32<T>(s_over_127));
+    return from_f32<T>(__fmul_rn((float)q, s));
+}
+
 // Dispatch a callable templated on the element type.
 #define MPSBNB_DISPATCH_DTYPE(dt, T, ...)                             \
     do {                                                              \

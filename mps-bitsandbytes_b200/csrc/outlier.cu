@@ -1,0 +1,117 @@
+// Outlier-aware INT8 linear (LLM.int8 mixed-precision decomposition), the forward of the reference's
+// OutlierAwareLinear (mps_bitsandbytes/nn/outlier_aware.py:84-146):
+//   y = deq(quantize_rowwise(x_main)) . deq(W_int8_main)^T  +  x_outlier . W_outlier^T  (+ bias)
+// where "main" are the input features that are not outlier columns, both dequantisations use a scale
+// rounded to the compute type first (`q.to(dtype) * (s / 127).to(dtype)`, :118-119, :138-139), and the
+// outlier columns of x meet weights kept in 16 bits.
+//
+// The reference slices columns out of x and W and runs two matrix products.  Here both parts share ONE
+// contraction over the full K: the operand built from x holds the re-quantised value in a main column and
+// the untouched 16-bit value in an outlier column; the operand built from W holds the dequantised int8
+// weight in a main column and the 16-bit outlier weight in an outlier column.  The tcgen05 GEMM then
+// accumulates main and outlier products together in fp32 (the reference rounds the two partial results to
+// 16 bits before adding them; the difference is far inside the 1e-2 matmul bound).  No gather, no second
+// GEMM, no addition pass.  With no outlier columns this is the pure INT8 path (:112-121).
+//
+// Workspace (caller-supplied): slot[K] int32 (0 = main column, j + 1 = outlier j), x operand
+// [M, ld8(K)], W operand [N, ld8(K)] in the compute type.
+#include "ops.cuh"
+
+namespace mpsbnb {
+
+static inline int64_t o_ld8(int64_t k) { return (k + 7) / 8 * 8; }
+static inline size_t o_align256(size_t b) { return (b + 255) / 256 * 256; }
+
+__global__ void outlier_slot_kernel(const int64_t *__restrict__ idx, int64_t n_out, int64_t K, int *__restrict__ slot) {
+    const int64_t j = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (j >= n_out) return;
+    const int64_t k = idx[j];
+    if (k >= 0 && k < K) slot[k] = (int)(j + 1);
+}
+
+// One CTA per row of x: row maximum over the main columns (clamped to 1e-8), then every main element is
+// quantised to int8 and expanded again, outlier elements are passed through in the compute type.
+template <typename TX, typename T>
+__global__ void __launch_bounds__(256) outlier_x_kernel(const TX *__restrict__ x, int64_t M, int64_t K,
+                                                        const int *__restrict__ slot, T *__restrict__ out, int64_t ld) {
+    __shared__ float red[8];
+    for (int64_t m = blockIdx.x; m < M; m += gridDim.x) {
+        const TX *row = x + m * K;
+        float a = 0.0f;
+        for (int64_t k = threadIdx.x; k < K; k += blockDim.x)
+            if (slot[k] == 0) a = fmaxf(a, fabsf(to_f32<TX>(row[k])));
+        a = fmaxf(cta_max(a, red), 1e-8f);
+        const float f = rdiv127(a);
+        const float s127 = __fdiv_rn(a, 127.0f);
+        for (int64_t k = threadIdx.x; k < K; k += blockDim.x) {
+            const float v = to_f32<TX>(row[k]);
+            out[m * ld + k] = slot[k] == 0 ? i8_times_rounded_scale<T>(quant_i8(v, f), s127) : from_f32<T>(v);
+        }
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) outlier_w_kernel(const int8_t *__restrict__ q, const float *__restrict__ scales,
+                                                        const T *__restrict__ outlier_w, int64_t n_out, int64_t N,
+                                                        int64_t K, const int *__restrict__ slot, T *__restrict__ out,
+                                                        int64_t ld) {
+    const int64_t total = N * K;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t n = i / K, k = i - n * K;
+        const int s = slot[k];
+        out[n * ld + k] = s == 0 ? i8_times_rounded_scale<T>(q[i], __fdiv_rn(__ldg(scales + n), 127.0f))
+                                 : outlier_w[n * n_out + (s - 1)];
+    }
+}
+
+static inline unsigned o_grid(int64_t items) {
+    const int64_t ctas = (items + 255) / 256, cap = (int64_t)sm_count() * 16;
+    return (unsigned)(ctas < 1 ? 1 : (ctas > cap ? cap : ctas));
+}
+
+}  // namespace mpsbnb
+
+using namespace mpsbnb;
+
+extern "C" size_t mpsbnb_outlier_linear_workspace_bytes(int64_t M, int64_t N, int64_t K) {
+    if (M <= 0 || N <= 0 || K <= 0) return 0;
+    return o_align256((size_t)K * 4) + o_align256((size_t)M * (size_t)o_ld8(K) * 2) + o_align256((size_t)N * (size_t)o_ld8(K) * 2);
+}
+
+extern "C" int mpsbnb_outlier_linear(const void *x, int x_dtype, int64_t M, const int8_t *W, const float *w_scales,
+                                     const int64_t *outlier_idx, int64_t n_outliers, const void *outlier_w,
+                                     int64_t N, int64_t K, const void *bias, int op_dtype, void *y, int y_dtype,
+                                     void *workspace, size_t workspace_bytes, void *stream) {
+    if (!valid_dtype(x_dtype) || !is_16bit(op_dtype) || !valid_dtype(y_dtype) || M < 0 || N < 0 || K <= 0 || n_outliers < 0)
+        return MPSBNB_ERR_INVALID_ARG;
+    if (M == 0 || N == 0) return MPSBNB_OK;
+    if (x == nullptr || W == nullptr || w_scales == nullptr || y == nullptr || workspace == nullptr) return MPSBNB_ERR_INVALID_ARG;
+    if (n_outliers > 0 && (outlier_idx == nullptr || outlier_w == nullptr)) return MPSBNB_ERR_INVALID_ARG;
+    if (workspace_bytes < mpsbnb_outlier_linear_workspace_bytes(M, N, K) || (reinterpret_cast<uintptr_t>(workspace) & 255) != 0)
+        return MPSBNB_ERR_WORKSPACE;
+    cudaStream_t st = (cudaStream_t)stream;
+    unsigned char *ws = reinterpret_cast<unsigned char *>(workspace);
+    int *slot = reinterpret_cast<int *>(ws);
+    ws += o_align256((size_t)K * 4);
+    void *xo = ws;
+    ws += o_align256((size_t)M * (size_t)o_ld8(K) * 2);
+    void *wo = ws;
+    const int64_t ld = o_ld8(K);
+    MPSBNB_CUDA_TRY(cudaMemsetAsync(slot, 0, (size_t)K * 4, st));
+    if (n_outliers > 0) {
+        outlier_slot_kernel<<<(unsigned)((n_outliers + 255) / 256), 256, 0, st>>>(outlier_idx, n_outliers, K, slot);
+        int rc = check_launch();
+        if (rc != MPSBNB_OK) return rc;
+    }
+    const unsigned xgrid = (unsigned)(M < (int64_t)sm_count() * 8 ? M : (int64_t)sm_count() * 8);
+    if (op_dtype == MPSBNB_F16) {
+        MPSBNB_DISPATCH_DTYPE(x_dtype, TX, (outlier_x_kernel<TX, __half><<<xgrid, 256, 0, st>>>((const TX *)x, M, K, slot, (__half *)xo, ld)));
+        outlier_w_kernel<__half><<<o_grid(N * K), 256, 0, st>>>(W, w_scales, (const __half *)outlier_w, n_outliers, N, K, slot, (__half *)wo, ld);
+    } else {
+        MPSBNB_DISPATCH_DTYPE(x_dtype, TX, (outlier_x_kernel<TX, __nv_bfloat16><<<xgrid, 256, 0, st>>>((const TX *)x, M, K, slot, (__nv_bfloat16 *)xo, ld)));
+        outlier_w_kernel<__nv_bfloat16><<<o_grid(N * K), 256, 0, st>>>(W, w_scales, (const __nv_bfloat16 *)outlier_w, n_outliers, N, K, slot, (__nv_bfloat16 *)wo, ld);
+    }
+    int rc = check_launch();
+    if (rc != MPSBNB_OK) return rc;
+    return gemm_16bit(xo, ld, wo, ld, op_dtype, M, N, K, nullptr, nullptr, bias, op_dtype, y, N, y_dtype, st);
+}

@@ -10,25 +10,6 @@
 
 namespace mpsbnb {
 
-__device__ __forceinline__ float rdiv127(float s) { return __fmul_rn(__frcp_rn(s), 127.0f); }
-
-__device__ __forceinline__ int8_t quant_i8(float x, float f) {
-    float v = rintf(__fmul_rn(x, f));                       // torch.round: half to even
-    return (int8_t)(int)fminf(fmaxf(v, -127.0f), 127.0f);
-}
-
-// CTA-wide max of non-negative values; every thread gets the result.
-__device__ __forceinline__ float cta_max(float a, float *red) {
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
-    __syncthreads();                                        // red[] may still be read by a previous use
-    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = a;
-    __syncthreads();
-    a = red[0];
-    for (int w = 1; w < (int)(blockDim.x >> 5); ++w) a = fmaxf(a, red[w]);
-    return a;
-}
-
 // ------------------------------------------------------------------ row statistics
 // One CTA per row: max|x| over the row (NOT clamped).
 template <typename T>

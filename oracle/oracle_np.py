@@ -371,3 +371,84 @@ def matmul_fp8_e4m3(x, codes, scales, bias=None, dtype="float16"):
     """mps_bitsandbytes/functional.py:796-807."""
     w = dequantize_fp8_e4m3(codes, scales, dtype)
     return linear(cast_to(np.asarray(x, dtype=np.float32), dtype), w, bias, dtype)
+
+
+# --------------------------------------------------------------------------- embeddings
+def mul_in(a: np.ndarray, b: np.ndarray, dtype: str) -> np.ndarray:
+    """Elementwise ``a * b`` for operands already rounded to ``dtype``, result rounded to
+    ``dtype`` (a torch multiply in float16 / bfloat16: the exact product rounded once)."""
+    return cast_to((np.asarray(a, dtype=np.float32) * np.asarray(b, dtype=np.float32)).astype(np.float32), dtype)
+
+
+def embedding_4bit(indices, packed, absmax, dim: int, blocksize: int = 64, quant_type: str = "nf4",
+                   dtype: str = "float16", padding_idx=None) -> np.ndarray:
+    """mps_bitsandbytes/nn/embedding.py:111-139 (the Python path): every looked-up row is
+    ``dequantize_4bit`` of that row alone (flat path, functional.py:388-416), rows equal to
+    ``padding_idx`` are zero.  ``packed`` [V, dim/2], ``absmax`` [V, ceil(dim/blocksize)]."""
+    idx = np.asarray(indices)
+    p = np.asarray(packed, dtype=np.uint8)
+    V = p.shape[0]
+    nb = (dim + blocksize - 1) // blocksize
+    Kp = padded_k(dim, blocksize)
+    full = np.zeros((V, Kp // 2), dtype=np.uint8)
+    full[:, :dim // 2] = p[:, :dim // 2]
+    table = dequantize_4bit(full, np.asarray(absmax, dtype=np.float32).reshape(V, nb), (V, dim), blocksize, quant_type, dtype)
+    out = table[idx.reshape(-1)].reshape(*idx.shape, dim).copy()
+    if padding_idx is not None:
+        out[idx == padding_idx] = 0
+    return out
+
+
+def embedding_8bit(indices, q, scales, dtype: str = "float16", padding_idx=None) -> np.ndarray:
+    """mps_bitsandbytes/nn/embedding.py:266-275: ``q.to(dtype) * (scales / 127.0).to(dtype)``
+    (the scale is rounded to ``dtype`` before the multiply), padding rows zero."""
+    idx = np.asarray(indices)
+    qi = np.asarray(q)[idx]
+    s = cast_to((np.asarray(scales, dtype=np.float32)[idx] / np.float32(127.0)).astype(np.float32), dtype)
+    out = mul_in(qi.astype(np.float32), np.asarray(s, dtype=np.float32)[..., None], dtype)
+    if padding_idx is not None:
+        out[idx == padding_idx] = 0
+    return out
+
+
+# --------------------------------------------------------------------------- outlier-aware int8 linear
+def outlier_from_linear(weight: np.ndarray, threshold: float = 6.0, dtype: str = "float16"):
+    """mps_bitsandbytes/nn/outlier_aware.py:184-207 for a weight already in ``dtype``:
+    outlier columns = col_max|w| > threshold * mean|w| (statistics rounded to ``dtype`` as torch
+    computes them on a 16-bit tensor: the mean is accumulated in fp32 and rounded once);
+    those columns are kept as they are and zeroed before the row-wise int8 quantisation.
+    Returns (weight_int8, weight_scales, outlier_indices, outlier_weights)."""
+    w = np.asarray(weight, dtype=np.float32)
+    col_max = np.abs(w).max(axis=0)
+    mean_abs = cast_to(np.array([np.abs(w).astype(np.float64).mean()], dtype=np.float32), dtype)[0]
+    limit = cast_to(np.array([np.float32(threshold) * np.float32(mean_abs)], dtype=np.float32), dtype)[0]
+    idx = np.where(col_max > np.float32(limit))[0].astype(np.int64)
+    w8 = w.copy()
+    w8[:, idx] = 0
+    q, s = quantize_rowwise(w8)
+    return q, s, idx, cast_to(w[:, idx], dtype)
+
+
+def outlier_linear(x, weight_int8, weight_scales, outlier_idx, outlier_w, bias=None, dtype: str = "float16"):
+    """mps_bitsandbytes/nn/outlier_aware.py:84-146.  Main columns: x is quantised row-wise, both
+    operands are dequantised as ``q.to(dtype) * (s / 127).to(dtype)`` and multiplied; outlier
+    columns: x (cast to ``dtype``) times the 16-bit outlier weights; the two results (each rounded
+    to ``dtype``) are added, then the bias is added, each addition rounded to ``dtype``."""
+    x = np.asarray(x)
+    K = x.shape[-1]
+    x2 = x.reshape(-1, K)
+    idx = np.asarray(outlier_idx, dtype=np.int64)
+    mask = np.ones(K, dtype=bool)
+    mask[idx] = False
+    xq, xs = quantize_rowwise(x2[:, mask])
+    xs_t = cast_to((xs / np.float32(127.0)).astype(np.float32), dtype)
+    x_fp = mul_in(xq.astype(np.float32), np.asarray(xs_t, dtype=np.float32)[:, None], dtype)
+    ws_t = cast_to((np.asarray(weight_scales, dtype=np.float32) / np.float32(127.0)).astype(np.float32), dtype)
+    w_fp = mul_in(np.asarray(weight_int8)[:, mask].astype(np.float32), np.asarray(ws_t, dtype=np.float32)[:, None], dtype)
+    y = linear(x_fp, w_fp, None, dtype)
+    if idx.size:
+        y_out = linear(cast_to(x2[:, idx].astype(np.float32), dtype), np.asarray(outlier_w, dtype=np.float32), None, dtype)
+        y = cast_to((np.asarray(y, dtype=np.float32) + np.asarray(y_out, dtype=np.float32)).astype(np.float32), dtype)
+    if bias is not None:
+        y = cast_to((np.asarray(y, dtype=np.float32) + np.asarray(bias, dtype=np.float32)[None, :]).astype(np.float32), dtype)
+    return y.reshape(*x.shape[:-1], -1)

@@ -2,11 +2,15 @@
 
 Usage (only where the reference checkout is available; it is pure Python + torch CPU):
 
-    python tests/golden/make_golden.py /path/to/mps-bitsandbytes
+    python tests/golden/make_golden.py /path/to/mps-bitsandbytes [--only-modules]
+
+(``--only-modules`` rewrites just ``golden_modules.npz`` and the ``ref_*.pt`` checkpoints.)
 
 It imports ``mps_bitsandbytes.functional`` from that path (the native extension is
 absent off macOS, so every call takes the reference's pure-PyTorch CPU code), feeds it
-seeded inputs and stores inputs and outputs in ``golden_*.npz``.  The fixtures pin the
+seeded inputs and stores inputs and outputs in ``golden_*.npz``; the module section also has
+the reference write real checkpoints (``ref_*.pt``: ``state_dict()`` of its Linear4bit /
+Linear8bit / Embedding4bit through ``torch.save``), which the drop-in modules must load.  The fixtures pin the
 numpy/C oracles (``tests/test_oracle_golden.py``) and, through them and directly, the
 CUDA kernels (``tests/test_gpu_*.py``).  bf16 tensors are stored as float32 (exact).
 
@@ -247,8 +251,142 @@ def main(ref_path):
     g["mod_l8"] = Linear8bit.from_linear(lin)(xin).detach().numpy()
     g["mod_f8"] = LinearFP8.from_linear(lin)(xin).detach().numpy()
     np.savez_compressed(f"{OUT}/golden_matmul.npz", **g)
+    modules(ref_path)
     print("golden fixtures written to", OUT)
 
 
+def modules(ref_path):
+    """Embeddings, the outlier-aware linear, the model-level helpers and on-disk checkpoints."""
+    if ref_path not in sys.path:
+        sys.path.insert(0, ref_path)
+    warnings.simplefilter("ignore")
+    import mps_bitsandbytes as ref
+    from mps_bitsandbytes.nn import (Embedding4bit, Embedding8bit, EmbeddingFP4, Linear4bit, Linear8bit,
+                                     OutlierAwareLinear)
+    g = {}
+    # ---- embeddings: (name, V, D, blocksize, quant_type, dtype, padding_idx)
+    torch.manual_seed(51)
+    ecases = [("e0", 50, 128, 64, "nf4", "float16", 3), ("e1", 37, 96, 32, "fp4", "float16", None),
+              ("e2", 20, 256, 64, "nf4", "bfloat16", 0), ("e3", 11, 64, 64, "fp4", "float32", None)]
+    for name, V, D, bs, qt, dt, pad in ecases:
+        emb = torch.nn.Embedding(V, D, padding_idx=pad).to(DT[dt])
+        emb.weight.data.mul_(0.3)
+        ids = torch.randint(0, V, (3, 7))
+        if pad is not None:
+            ids[0, 2] = pad; ids[2, 5] = pad
+        e4 = Embedding4bit.from_embedding(emb, quant_type=qt, blocksize=bs)
+        e8 = Embedding8bit.from_embedding(emb)
+        g[name + "_w"] = npy(emb.weight.data); g[name + "_ids"] = ids.numpy()
+        g[name + "_packed"] = e4.weight_packed.numpy(); g[name + "_absmax"] = e4.weight_absmax.numpy()
+        g[name + "_out4"] = npy(e4(ids)); g[name + "_q8"] = e8.weight_int8.numpy(); g[name + "_s8"] = e8.weight_scales.numpy()
+        g[name + "_out8"] = npy(e8(ids))
+    g["ecases"] = np.array([[str(v) for v in c] for c in ecases], dtype=str)
+    e4 = EmbeddingFP4.from_embedding(torch.nn.Embedding(9, 64).half())
+    assert e4.quant_type == "fp4"
+    # ---- outlier-aware linear: (name, M, N, K, dtype, bias, outlier columns planted in W, in x)
+    torch.manual_seed(52)
+    ocases = [("o0", 6, 40, 96, "float16", True, 3), ("o1", 5, 24, 64, "float16", False, 0),
+              ("o2", 9, 32, 128, "bfloat16", True, 5), ("o3", 130, 72, 200, "float16", True, 4)]
+    for name, M, N, K, dt, bias, nout in ocases:
+        lin = torch.nn.Linear(K, N, bias=bias)
+        lin.weight.data.mul_(0.2)
+        cols = torch.randperm(K)[:nout]
+        lin.weight.data[:, cols] *= 12.0
+        lin = lin.to(DT[dt])
+        layer = OutlierAwareLinear.from_linear(lin, threshold=6.0)
+        assert len(layer.outlier_indices) == nout, (name, len(layer.outlier_indices))
+        x = torch.randn(2, M, K)
+        x[..., cols] *= 20.0
+        x = x.to(DT[dt])
+        g[name + "_w"] = npy(lin.weight.data); g[name + "_x"] = npy(x)
+        if bias: g[name + "_b"] = npy(lin.bias.data)
+        g[name + "_q"] = layer.weight_int8.numpy(); g[name + "_s"] = layer.weight_scales.numpy()
+        g[name + "_idx"] = layer.outlier_indices.numpy(); g[name + "_ow"] = npy(layer.outlier_weights)
+        g[name + "_y"] = npy(layer(x))
+    g["ocases"] = np.array([[str(v) for v in c] for c in ocases], dtype=str)
+    # fp32 activations into an fp16 layer (the row-wise quantiser then sees fp32 values)
+    lin = torch.nn.Linear(64, 16).half()
+    lin.weight.data[:, 7] *= 30
+    layer = OutlierAwareLinear.from_linear(lin)
+    x32 = torch.randn(4, 64)
+    g["o32_w"] = lin.weight.data.numpy(); g["o32_b"] = lin.bias.data.numpy(); g["o32_x"] = x32.numpy()
+    g["o32_idx"] = layer.outlier_indices.numpy(); g["o32_y"] = layer(x32).numpy()
+    # ---- model-level helpers on a small two-block model
+    torch.manual_seed(53)
+
+    class Block(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.q_proj = torch.nn.Linear(64, 64)
+            self.mlp = torch.nn.Sequential(torch.nn.Linear(64, 128), torch.nn.GELU(), torch.nn.Linear(128, 64))
+            self.norm = torch.nn.LayerNorm(64)
+
+        def forward(self, h):
+            return self.norm(h + self.mlp(self.q_proj(h)))
+
+    class Toy(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.embed = torch.nn.Embedding(30, 64)
+            self.layers = torch.nn.ModuleList([Block(), Block()])
+            self.lm_head = torch.nn.Linear(64, 30, bias=False)
+
+        def forward(self, ids):
+            h = self.embed(ids)
+            for layer in self.layers:
+                h = layer(h)
+            return self.lm_head(h)
+
+    torch.manual_seed(55)
+    base = Toy().half()
+    ids = torch.randint(0, 30, (2, 5))
+    g["toy_ids"] = ids.numpy()
+    for k_, v_ in base.state_dict().items():
+        g["toy_sd_" + k_] = v_.numpy()
+    g["toy_keys"] = np.array(list(base.state_dict().keys()), dtype=str)
+    import copy
+    m4 = ref.quantize_model(copy.deepcopy(base), ref.BitsAndBytesConfig(load_in_4bit=True, bnb_4bit_quant_type="fp4"),
+                            device="cpu", modules_to_not_convert=["lm_head"])
+    g["toy_y4"] = m4(ids).detach().numpy()
+    g["toy_types4"] = np.array([f"{n}:{type(m).__name__}" for n, m in m4.named_modules() if "Linear" in type(m).__name__], dtype=str)
+    fp = ref.get_memory_footprint(m4)
+    g["toy_fp4"] = np.array([fp["total_params"], fp["quantized_params"], fp["fp16_size_gb"], fp["actual_size_gb"]], dtype=np.float64)
+    m8 = ref.quantize_model(copy.deepcopy(base), load_in_8bit=True, device="cpu")
+    g["toy_y8"] = m8(ids).detach().numpy()
+    g["toy_types8"] = np.array([f"{n}:{type(m).__name__}" for n, m in m8.named_modules() if "Linear" in type(m).__name__], dtype=str)
+    fp = ref.get_memory_footprint(m8)
+    g["toy_fp8"] = np.array([fp["total_params"], fp["quantized_params"], fp["fp16_size_gb"], fp["actual_size_gb"]], dtype=np.float64)
+    cfg = ref.BitsAndBytesConfig(load_in_4bit=True, bnb_4bit_compute_dtype=torch.bfloat16, llm_int8_skip_modules=["lm_head"])
+    g["cfg_dict"] = np.array([f"{k}={v}" for k, v in cfg.to_dict().items()], dtype=str)
+    back = ref.BitsAndBytesConfig.from_dict(cfg.to_dict())
+    g["cfg_back_dtype"] = np.array(str(back.bnb_4bit_compute_dtype))
+    g["cfg_method"] = np.array([cfg.quantization_method, ref.BitsAndBytesConfig(load_in_8bit=True).quantization_method,
+                                ref.BitsAndBytesConfig().quantization_method], dtype=str)
+    # ---- checkpoints written by the reference
+    torch.manual_seed(56)
+    lin = torch.nn.Linear(128, 48).half()
+    xin = torch.randn(4, 128).half()
+    l4 = Linear4bit.from_linear(lin, quant_type="nf4", compress_statistics=True)
+    torch.save(l4.state_dict(), f"{OUT}/ref_linear4bit_nf4_dq.pt")
+    l4b = Linear4bit.from_linear(lin, quant_type="fp4", blocksize=32)
+    torch.save(l4b.state_dict(), f"{OUT}/ref_linear4bit_fp4_bs32.pt")
+    l8 = Linear8bit.from_linear(lin)
+    torch.save(l8.state_dict(), f"{OUT}/ref_linear8bit.pt")
+    emb = torch.nn.Embedding(40, 128).half()
+    e4 = Embedding4bit.from_embedding(emb)
+    torch.save(e4.state_dict(), f"{OUT}/ref_embedding4bit.pt")
+    eids = torch.randint(0, 40, (6,))
+    g["ck_x"] = xin.numpy(); g["ck_l4"] = l4(xin).detach().numpy(); g["ck_l4b"] = l4b(xin).detach().numpy()
+    g["ck_l8"] = l8(xin).detach().numpy(); g["ck_eids"] = eids.numpy(); g["ck_e4"] = e4(eids).numpy()
+    g["ck_l4_deq"] = l4.dequantize().numpy()
+    np.savez_compressed(f"{OUT}/golden_modules.npz", **g)
+    print("module fixtures written")
+
+
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    args = [a for a in sys.argv[1:] if not a.startswith("--")]
+    path = args[0] if args else "/root/reference"
+    if "--only-modules" in sys.argv:
+        modules(path)
+    else:
+        main(path)
