@@ -1,7 +1,7 @@
 """Benchmark of the fused dequantise-matmul hot path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--batch M]
-                    [--layers L] [--skip-extras] [--prefill-only]
+                    [--layers L] [--skip-extras] [--prefill-only] [--int8-only]
 
 Workload (N = 1): the Llama-2-7B-shaped NF4 decode stack of BASELINE config 3 — 32 layers x
 {q,k,v,o 4096x4096, gate/up 11008x4096, down 4096x11008}, double-quantised absmax, fp16,
@@ -15,7 +15,8 @@ work shrinks with N (strong scaling of a fixed model).
 Prints ONE JSON line: metric nf4_decode_gbs = algorithmic bytes per step / step time, with
 the HBM roofline, an end-to-end figure through the public LayerStack API with host buffers,
 a CPU baseline (the C oracle of the reference's CPU path on this host's cores), and, at
-N = 1, the prefill GEMM of BASELINE config 2 (FP4, 2048 x 4096 x 11008) as a second object.
+N = 1, the prefill GEMM of BASELINE config 2 (FP4, 2048 x 4096 x 11008) as a second object and
+the INT8 / FP8 / outlier-split matmuls of BASELINE config 4 (512 x 4096 x 16384) as a third.
 
 --layers L runs a stack of only L layers (a reduced workload for profiler captures; the JSON
 line names it) and --skip-extras leaves out the prefill object and the CPU baseline.  The timed
@@ -203,6 +204,49 @@ def prefill_config2(torch, peaks, steps=20, warmup=5):
                          "frac": tf / peaks["bf16_tflops"], "traffic": None, "peak_source": peaks["source"]}}
 
 
+def int8_fp8_config4(torch, peaks, steps=10, warmup=3):
+    """BASELINE config 4: activations [512, 4096] fp16 with 0.5 % of the columns at magnitude ~20, weight
+    4096 x 16384 ~ N(0, 0.02): matmul_int8 (row-wise A, column-wise B), matmul_colrow, matmul_fp8_e4m3 and the
+    outlier-aware split (OutlierAwareLinear).  Every figure includes the operand-preparation passes."""
+    import mps_bitsandbytes_b200 as bnb
+    M, K, Nn = 512, 4096, 16384
+    g = torch.Generator(device="cuda"); g.manual_seed(4)
+    w = (torch.randn(Nn, K, device="cuda", generator=g) * 0.02).half()
+    x = torch.randn(M, K, device="cuda", generator=g).half()
+    cols = torch.randperm(K, device="cuda", generator=g)[: K // 200]
+    x[:, cols] *= 20.0
+    w_out = w.clone(); w_out[:, cols] *= 15.0                      # the same columns large in the weight: detected as outliers
+    aq, a_s = bnb.quantize_rowwise(x)
+    bq_t, b_s = bnb.quantize_rowwise(w)                             # per output column of B = per row of W
+    bq = bq_t.t().contiguous()                                      # [K, N], N contiguous
+    cq, cr, cc = bnb.quantize_colrow(w)
+    f8, f8s = bnb.quantize_fp8_e4m3(w)
+    lin = torch.nn.Linear(K, Nn, bias=False, device="cuda", dtype=torch.float16)
+    lin.weight.data = w_out
+    oal = bnb.OutlierAwareLinear.from_linear(lin)
+    del lin, w, w_out, bq_t
+    cases = {"matmul_int8": lambda: bnb.matmul_int8(aq, bq, a_s, b_s),
+             "matmul_colrow": lambda: bnb.matmul_colrow(x, cq, cr, cc),
+             "matmul_fp8_e4m3": lambda: bnb.matmul_fp8_e4m3(x, f8, f8s),
+             "outlier_aware_linear": lambda: oal(x)}
+    flops = 2.0 * M * K * Nn
+    res = {"config": {"workload": f"x [{M},{K}] fp16 (0.5% outlier columns), weight {K}x{Nn}; dequantise/requantise passes + tcgen05 GEMM",
+                      "outlier_columns": int(oal.outlier_indices.numel())}, "unit": "TFLOP/s", "peak": peaks["bf16_tflops"]}
+    for name, fn in cases.items():
+        for _ in range(warmup):
+            fn()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / steps
+        res[name] = {"ms": ms, "tflops": flops / (ms * 1e-3) / 1e12, "frac": flops / (ms * 1e-3) / 1e12 / peaks["bf16_tflops"]}
+    return res
+
+
 def run_gpu(args, cfg):
     import torch
     import torch.distributed as dist
@@ -306,6 +350,10 @@ def run_gpu(args, cfg):
                 out["prefill"] = prefill_config2(torch, peaks)
             except Exception as ex:                                  # reported, never hidden
                 out["prefill"] = {"error": repr(ex)}
+            try:
+                out["int8_fp8"] = int8_fp8_config4(torch, peaks)
+            except Exception as ex:
+                out["int8_fp8"] = {"error": repr(ex)}
             out["cpu_baseline"] = cpu_baseline(cfg, M)
         print(json.dumps(out), flush=True)
     if world > 1:
@@ -326,19 +374,23 @@ def main():
     ap.add_argument("--layers", type=int, default=None, help="reduced depth, for profiler captures")
     ap.add_argument("--skip-extras", action="store_true", help="no prefill object, no CPU baseline")
     ap.add_argument("--prefill-only", action="store_true", help="only the prefill GEMM object (BASELINE config 2)")
+    ap.add_argument("--int8-only", action="store_true", help="only the INT8 / FP8 / outlier-split object (BASELINE config 4)")
     ap.add_argument("--exchange", default="fused", choices=["fused", "nccl"],
                     help="N > 1: layer boundary by peer stores + flags (default) or by an NCCL all-gather")
     ap.add_argument("--boundary", default=None, choices=["kernel", "inline", "stream"],
                     help="layer boundary: its own small kernel, the closing step of the GEMV launch, or streamed tile "
                          "by tile from inside the launch (default)")
     ap.add_argument("--per-layer", action="store_true", help="one GEMV launch per layer instead of one per step")
-    ap.add_argument("--no-mid-tc", action="store_true", help="batch 9..16: per-linear launches of the older kernel instead of tcgen05")
+    ap.add_argument("--no-mid-tc", action="store_true", help="batch 9..32: per-linear launches of the older kernel instead of tcgen05")
     args = ap.parse_args()
     from mps_bitsandbytes_b200 import stack as S
     cfg = S.LLAMA2_7B if args.model == "llama2-7b" else S.LLAMA_70B
     if args.prefill_only:
         import torch
         print(json.dumps(prefill_config2(torch, load_peaks(), steps=args.steps, warmup=max(args.warmup, 3))))
+    elif args.int8_only:
+        import torch
+        print(json.dumps(int8_fp8_config4(torch, load_peaks(), steps=args.steps, warmup=max(args.warmup, 3))))
     elif args.impl == "reference":
         run_reference(args, cfg)
     else:

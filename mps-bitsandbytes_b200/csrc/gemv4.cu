@@ -417,7 +417,7 @@ extern "C" int mpsbnb_gemv_4bit(const void *x, int x_dtype, int64_t M, const uin
         p.K = 0;
     }
     cudaStream_t st = (cudaStream_t)stream;
-    if (M <= 16 && K > 0 && aligned16(packed) && decode_uses_tensor_path())  // TMA ring + tcgen05 (batch <= 16)
+    if (M <= 32 && K > 0 && aligned16(packed) && decode_uses_tensor_path())  // TMA ring + tcgen05 (batch <= 32)
         return gemv4_tc_single(x, x_dtype, M, packed, absmax, absmax2, N, K, quant_type, bias, y, y_dtype, st);
     if (M <= 8 && K > 0 && aligned16(packed))                  // TMA ring + mma.sync
         return gemv4_stream_single(x, x_dtype, M, packed, absmax, absmax2, N, K, quant_type, bias, y, y_dtype, st);

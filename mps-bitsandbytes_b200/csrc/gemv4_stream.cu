@@ -1034,7 +1034,7 @@ int gemv4_stream_single(const void *x, int x_dtype, int64_t M, const uint8_t *pa
 using namespace mpsbnb;
 
 extern "C" int mpsbnb_decode_kernel_select(int which) { return decode_kernel_select(which); }
-extern "C" int mpsbnb_gemv_4bit_group_max_m(void) { return decode_uses_tensor_path() ? 16 : SG_MAX_M; }
+extern "C" int mpsbnb_gemv_4bit_group_max_m(void) { return decode_uses_tensor_path() ? 32 : SG_MAX_M; }
 
 // ------------------------------------------------------------------------------------------
 // grouped launches: a plan (device memory supplied by the caller) holds the linears and units
@@ -1065,7 +1065,7 @@ extern "C" int mpsbnb_gemv_4bit_group_plan(const mpsbnb_linear4_desc *descs, int
                                            mpsbnb_group_plan *plan_out, void *stream) {
     if (descs == nullptr || n_linears <= 0 || plan_dev == nullptr || plan_out == nullptr) return MPSBNB_ERR_INVALID_ARG;
     if (!is_16bit(x_dtype) || !valid_dtype(y_dtype) || (quant_type != MPSBNB_NF4 && quant_type != MPSBNB_FP4)) return MPSBNB_ERR_INVALID_ARG;
-    if (M <= 0 || M > (decode_uses_tensor_path() ? 16 : SG_MAX_M)) return MPSBNB_ERR_UNSUPPORTED;
+    if (M <= 0 || M > (decode_uses_tensor_path() ? 32 : SG_MAX_M)) return MPSBNB_ERR_UNSUPPORTED;
     if ((reinterpret_cast<uintptr_t>(plan_dev) & 255) != 0) return MPSBNB_ERR_INVALID_ARG;
     if (decode_uses_tensor_path())
         return tc_plan(descs, n_linears, M, x_dtype, y_dtype, quant_type, plan_dev, plan_bytes, plan_out, (cudaStream_t)stream);

@@ -39,21 +39,23 @@ constexpr int TG_CONSUMERS = 16;
 constexpr int TG_WARP_PRODUCER = 16, TG_WARP_MMA = 17, TG_WARP_LOADER0 = 18, TG_LOADERS = 2, TG_WARP_EPI0 = 20;
 constexpr int TG_THREADS = 24 * 32;
 constexpr int TG_ROWS = 128;                               // weight rows per tile = UMMA M
-constexpr int TG_N = 16;                                   // UMMA N (batch rows padded)
 constexpr int TG_STAGE_BLOCKS = 4;                         // quantisation blocks (64 k) per stage
 constexpr int TG_STAGE_K = TG_STAGE_BLOCKS * 64;
 constexpr int TG_W_BYTES = TG_ROWS * TG_STAGE_K / 2;       // 16384
-constexpr int TG_X_BYTES = TG_N * TG_STAGE_K * 2;          // 8192: four [16 x 64] atoms of 2048 B
 constexpr int TG_A_BYTES = TG_STAGE_BLOCKS * TG_ROWS * 4;  // 2048: fp32 scale [row][block], or int8 codes [row] + fp32 maxima [row]
-constexpr int TG_XS_BYTES = TG_X_BYTES + TG_A_BYTES;
 constexpr int TG_NXS = 4;                                  // scale/x slots (a multiple of TG_LOADERS: one loader per slot)
 constexpr int TG_MAX_SLOTS = 9;
 constexpr int TG_ABUFS = 3;                                // A tiles in tensor memory (128 columns each)
-constexpr int TG_MAX_M = 16;                               // batch rows: the UMMA N
+constexpr int TG_MAX_M = 32;                               // largest batch (the 32-column instance)
 constexpr uint32_t TG_LUT_ABS = 131072u;                   // table at an absolute shared address: see expander
 constexpr uint32_t TG_HIGH_ABS = TG_LUT_ABS + 65536u;      // entry b of lane l sits at b * 256 + l * 4: a 64 KiB span
 constexpr int TG_SMEM_BYTES = 227 * 1024;
 constexpr uint32_t TG_TMEM_COLS = 512, TG_D_COL0 = TG_ABUFS * 128;
+// Consecutive K steps add into tg_dsplit(NB) DIFFERENT accumulators (step j -> accumulator j % split), which
+// the epilogue sums: an MMA of this small shape is bound by the latency of its read-modify-write of the
+// accumulator, and MMAs on independent accumulators need not wait for each other.
+// (two accumulator buffers of NB * split columns each fit the 128 columns left beside the A tiles.)
+__host__ __device__ constexpr int tg_dsplit(int nb) { return 64 / nb; }
 static_assert(TG_NXS % TG_LOADERS == 0, "each scale/x slot must belong to exactly one loader warp");
 
 static __device__ int g_tc_status = 0;
@@ -132,8 +134,14 @@ struct TgSlots {
     }
 };
 
-template <typename XT>
+template <typename XT, int NB>
 __global__ void __launch_bounds__(TG_THREADS, 1) gemv4_tc_kernel(const __grid_constant__ TcArgs a) {
+    // NB = batch rows the x tile and the accumulators hold (the UMMA N): 16 or 32
+    constexpr int X_BYTES = NB * TG_STAGE_K * 2;                     // four [NB x 64] atoms of NB * 128 bytes
+    constexpr int XS_BYTES = X_BYTES + TG_A_BYTES;
+    constexpr int DSPLIT = tg_dsplit(NB);
+    constexpr uint32_t D_STRIDE = NB * DSPLIT;                       // columns per accumulator buffer
+    static_assert(TG_D_COL0 + 2 * D_STRIDE <= TG_TMEM_COLS && TG_STAGE_K / 16 >= DSPLIT, "accumulators fit; the first stage initialises all");
     extern __shared__ __align__(1024) unsigned char smem[];
     const uint32_t s_base = smem_u32(smem);
     // barriers: full[9] empty[9] xfull[4] xempty[4] afull[3] aempty[3] dfull[2] dempty[2]; then the TMEM
@@ -153,7 +161,7 @@ __global__ void __launch_bounds__(TG_THREADS, 1) gemv4_tc_kernel(const __grid_co
 
     const uint32_t s_xs = (s_bar + 512u + 1023u) & ~1023u;            // scale/x ring: [x tile 8 KiB][scales 2 KiB] per slot
     TgSlots sm;
-    sm.low0 = s_xs + (uint32_t)(TG_NXS * TG_XS_BYTES);
+    sm.low0 = s_xs + (uint32_t)(TG_NXS * XS_BYTES);
     sm.high0 = TG_HIGH_ABS;
     sm.nlow = (int)((TG_LUT_ABS - sm.low0) / TG_W_BYTES);
     {
@@ -191,7 +199,7 @@ __global__ void __launch_bounds__(TG_THREADS, 1) gemv4_tc_kernel(const __grid_co
             tg_sts32(TG_LUT_ABS + (uint32_t)((warp * 32 + j) * 256 + lane * 4), __shfl_sync(0xffffffffu, mine, j));
     } else if (warp < 16) {
         // the scale/x ring starts as zeros: batch rows >= M of every x tile are never written
-        const int total = TG_NXS * TG_XS_BYTES;
+        const int total = TG_NXS * XS_BYTES;
         for (int o = (tid - 256) * 16; o < total; o += 256 * 16) tg_sts128(s_xs + o, make_uint4(0u, 0u, 0u, 0u));
     } else if (warp == TG_WARP_MMA) {
         tmem_alloc(s_holder, TG_TMEM_COLS);
@@ -235,7 +243,7 @@ __global__ void __launch_bounds__(TG_THREADS, 1) gemv4_tc_kernel(const __grid_co
     } else if (warp == TG_WARP_MMA) {
         // ------------------------------------------------------------ MMA issue
         if (lane == 0) {
-            constexpr uint32_t idesc = umma_idesc_f16(tg_fmt<XT>(), TG_ROWS, TG_N);
+            constexpr uint32_t idesc = umma_idesc_f16(tg_fmt<XT>(), TG_ROWS, NB);
             int abuf = 0, xslot = 0, dcount = 0;
             uint32_t aph = 0, xph = 0;
             bool ok = true;
@@ -243,19 +251,20 @@ __global__ void __launch_bounds__(TG_THREADS, 1) gemv4_tc_kernel(const __grid_co
                 const TcPiece pc = piece_of(p);
                 const int d = dcount & 1;
                 if (!mbar_wait_sleep(dempty_bar(d), (((uint32_t)dcount >> 1) & 1u) ^ 1u, abort_flag, kSleepFast)) { atomicExch(&g_tc_status, 402); *abort_flag = 1; break; }
-                const uint32_t tmem_d = tmem_base + TG_D_COL0 + (uint32_t)(TG_N * d);
+                const uint32_t tmem_d = tmem_base + TG_D_COL0 + D_STRIDE * (uint32_t)d;
                 for (int s = pc.s_begin; s < pc.s_end; ++s) {
                     if (!mbar_wait_sleep(xfull_bar(xslot), xph, abort_flag, kSleepFast)) { atomicExch(&g_tc_status, 403); *abort_flag = 1; ok = false; break; }
                     if (!mbar_wait_sleep(afull_bar(abuf), aph, abort_flag, kSleepFast)) { atomicExch(&g_tc_status, 404); *abort_flag = 1; ok = false; break; }
                     tc_fence_after();
                     fence_proxy_async_smem();                            // the x tile was written through the generic proxy
-                    const uint64_t xdesc = umma_desc_k_sw128(s_xs + (uint32_t)(xslot * TG_XS_BYTES));
+                    const uint64_t xdesc = umma_desc_k_sw128(s_xs + (uint32_t)(xslot * XS_BYTES));
                     const uint32_t tmem_a = tmem_base + (uint32_t)(abuf * 128);
 #pragma unroll
                     for (int j = 0; j < TG_STAGE_K / 16; ++j) {
                         // K step j: 8 columns of the A tile; 32 bytes further in the 128-byte row of atom j / 4
-                        const uint64_t bd = xdesc + (uint64_t)((((j >> 2) * 2048) + (j & 3) * 32) >> 4);
-                        umma_f16_tmem_a(tmem_d, tmem_a + (uint32_t)(8 * j), bd, idesc, s > pc.s_begin || j > 0);
+                        const uint64_t bd = xdesc + (uint64_t)((((j >> 2) * (NB * 128)) + (j & 3) * 32) >> 4);
+                        umma_f16_tmem_a(tmem_d + (uint32_t)(NB * (j % DSPLIT)), tmem_a + (uint32_t)(8 * j), bd, idesc,
+                                        s > pc.s_begin || j >= DSPLIT);
                     }
                     umma_commit(aempty_bar(abuf));
                     umma_commit(xempty_bar(xslot));
@@ -281,16 +290,31 @@ __global__ void __launch_bounds__(TG_THREADS, 1) gemv4_tc_kernel(const __grid_co
             const int d = dcount & 1;
             if (!mbar_wait_sleep(dfull_bar(d), ((uint32_t)dcount >> 1) & 1u, abort_flag, kSleepSlow)) { atomicExch(&g_tc_status, 405); *abort_flag = 1; break; }
             tc_fence_after();
-            uint32_t v[16];
-            {
-                uint32_t lo[8], hi[8];
-                const uint32_t taddr = tmem_base + ((uint32_t)(32 * e) << 16) + TG_D_COL0 + (uint32_t)(TG_N * d);
-                tmem_ld_32x8(taddr, lo);
-                if (a.M > 8) tmem_ld_32x8(taddr + 8u, hi);
+            float v[NB];
 #pragma unroll
-                for (int i = 0; i < 8; ++i) { v[i] = lo[i]; v[8 + i] = a.M > 8 ? hi[i] : 0u; }
+            for (int i = 0; i < NB; ++i) v[i] = 0.0f;
+            {
+                const uint32_t taddr = tmem_base + ((uint32_t)(32 * e) << 16) + TG_D_COL0 + D_STRIDE * (uint32_t)d;
+#pragma unroll
+                for (int q = 0; q < DSPLIT; ++q) {
+                    uint32_t part[NB];
+#pragma unroll
+                    for (int c = 0; c < NB / 8; ++c) {
+                        uint32_t r8[8];
+                        if (a.M > 8 * c) {
+                            tmem_ld_32x8(taddr + (uint32_t)(NB * q + 8 * c), r8);
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) part[8 * c + i] = r8[i];
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) part[8 * c + i] = 0u;
+                        }
+                    }
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < NB; ++i) v[i] += __uint_as_float(part[i]);
+                }
             }
-            tmem_ld_wait();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(dempty_bar(d));
@@ -306,15 +330,15 @@ __global__ void __launch_bounds__(TG_THREADS, 1) gemv4_tc_kernel(const __grid_co
             if (acc != nullptr) {
                 if (mine)
 #pragma unroll
-                    for (int m = 0; m < TG_MAX_M; ++m) if (m < a.M) atomicAdd(acc + (int64_t)m * LN + n, __uint_as_float(v[m]) + (pc.s_begin == 0 ? bv : 0.0f));
+                    for (int m = 0; m < NB; ++m) if (m < a.M) atomicAdd(acc + (int64_t)m * LN + n, v[m] + (pc.s_begin == 0 ? bv : 0.0f));
             } else if (pc.parts == 1) {
                 if (mine)
 #pragma unroll
-                    for (int m = 0; m < TG_MAX_M; ++m) if (m < a.M) store_y(m, __uint_as_float(v[m]) + bv);
+                    for (int m = 0; m < NB; ++m) if (m < a.M) store_y(m, v[m] + bv);
             } else {
                 if (mine)
 #pragma unroll
-                    for (int m = 0; m < TG_MAX_M; ++m) if (m < a.M) atomicAdd(ws + (int64_t)m * LN + n, __uint_as_float(v[m]));
+                    for (int m = 0; m < NB; ++m) if (m < a.M) atomicAdd(ws + (int64_t)m * LN + n, v[m]);
                 __threadfence();
                 __syncwarp();
                 int old = 0;
@@ -425,8 +449,8 @@ __global__ void __launch_bounds__(TG_THREADS, 1) gemv4_tc_kernel(const __grid_co
             more = advance_to_mine();
             if (more && !L->scale_async) read_scales(L, pc.row0, s, nxt);
             if (!mbar_wait_sleep(xempty_bar(my_x), my_ph ^ 1u, abort_flag, kSleepSlow)) { atomicExch(&g_tc_status, 406); *abort_flag = 1; break; }
-            const uint32_t xb = s_xs + (uint32_t)(my_x * TG_XS_BYTES);
-            const uint32_t ab = xb + TG_X_BYTES;
+            const uint32_t xb = s_xs + (uint32_t)(my_x * XS_BYTES);
+            const uint32_t ab = xb + X_BYTES;
             if (my_async) {
                 // scales: nothing passes through registers, so this warp never waits for global memory and runs
                 // as far ahead as the ring allows.  Row n gets its four codes (or floats) and its second-level maximum.
@@ -460,15 +484,25 @@ __global__ void __launch_bounds__(TG_THREADS, 1) gemv4_tc_kernel(const __grid_co
             }
             // x tile: row m of atom (lane >> 3) (rows 8..15 are the second 8-row group, 1 KiB further), 16-byte chunk
             // (lane & 7) ^ (m & 7)  (128-byte swizzle)
-            for (int m = 0; m < a.M; ++m) {
-                const uint32_t dst = xb + (uint32_t)((lane >> 3) * 2048 + (m >> 3) * 1024 + (m & 7) * 128 + (((lane & 7) ^ (m & 7)) << 4));
-                if (my_L->x_vec_ok) {
-                    const int k0 = my_s * TG_STAGE_K + lane * 8;
-                    const bool in = k0 < my_L->K;
-                    const XT *xr = reinterpret_cast<const XT *>(my_L->x) + (int64_t)m * my_L->x_ld;
-                    tg_cp_async16(dst, xr + (in ? k0 % my_L->x_period : 0), in ? 16u : 0u);
+            // Everything that does not depend on m is computed once: the asynchronous copies below are "memory"
+            // operations to the compiler, so a load or the 64-bit modulo left inside the loop would be redone for
+            // every batch row (that made the loaders the limit of the kernel from batch 8 up).
+            {
+                const int k0 = my_s * TG_STAGE_K + lane * 8;
+                const bool vec = my_L->x_vec_ok != 0;
+                const bool in = k0 < my_L->K;
+                const int64_t ld = my_L->x_ld;
+                const XT *src = reinterpret_cast<const XT *>(my_L->x) + (in && vec ? k0 % my_L->x_period : 0);
+                const uint32_t nbytes = in ? 16u : 0u;
+                const uint32_t dst0 = xb + (uint32_t)((lane >> 3) * (NB * 128));
+                const int M = a.M;
+                if (vec) {
+#pragma unroll 4
+                    for (int m = 0; m < M; ++m, src += ld)
+                        tg_cp_async16(dst0 + (uint32_t)((m >> 3) * 1024 + (m & 7) * 128 + (((lane & 7) ^ (m & 7)) << 4)), src, nbytes);
                 } else {
-                    tg_sts128(dst, read_x(my_L, my_s, m));
+                    for (int m = 0; m < M; ++m)
+                        tg_sts128(dst0 + (uint32_t)((m >> 3) * 1024 + (m & 7) * 128 + (((lane & 7) ^ (m & 7)) << 4)), read_x(my_L, my_s, m));
                 }
             }
             fence_proxy_async_smem();
@@ -504,7 +538,7 @@ __global__ void __launch_bounds__(TG_THREADS, 1) gemv4_tc_kernel(const __grid_co
         auto expand = [&](const uint4 &lo, const uint4 &hi) {
             if (!mbar_wait_sleep(xfull_bar(xslot), xph, abort_flag, kSleepFast)) { atomicExch(&g_tc_status, 408); *abort_flag = 1; ok = false; return; }
             // my (row, block) scale: fp32 [row][4], or int8 codes [row] + second-level maximum [row]
-            const uint32_t ab = s_xs + (uint32_t)(xslot * TG_XS_BYTES) + TG_X_BYTES;
+            const uint32_t ab = s_xs + (uint32_t)(xslot * XS_BYTES) + X_BYTES;
             float scale;
             if (tg_lds_u32(s_mode + 4u * xslot) != 0u) {
                 const int code = (int)(int8_t)((tg_lds_u32(ab + (uint32_t)(row * 4)) >> (8 * b)) & 0xFFu);
@@ -612,14 +646,14 @@ static int tc_fill_linear(TcLinear &L, const TcHostLinear &h, int y_dtype) {
     return MPSBNB_OK;
 }
 
-template <typename XT>
-static int tc_launch(TcArgs &args, int grid, cudaStream_t st, bool pdl) {
+template <typename XT, int NB>
+static int tc_launch_nb(TcArgs &args, int grid, cudaStream_t st, bool pdl) {
     args.zero = 0u;
     static int configured[64] = {};
     int dev = 0;
     MPSBNB_CUDA_TRY(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64 || !configured[dev]) {
-        MPSBNB_CUDA_TRY(cudaFuncSetAttribute(gemv4_tc_kernel<XT>, cudaFuncAttributeMaxDynamicSharedMemorySize, TG_SMEM_BYTES));
+        MPSBNB_CUDA_TRY(cudaFuncSetAttribute(gemv4_tc_kernel<XT, NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, TG_SMEM_BYTES));
         if (dev >= 0 && dev < 64) configured[dev] = 1;
     }
     cudaLaunchConfig_t cfg;
@@ -629,8 +663,13 @@ static int tc_launch(TcArgs &args, int grid, cudaStream_t st, bool pdl) {
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr; cfg.numAttrs = pdl ? 1 : 0;
-    MPSBNB_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemv4_tc_kernel<XT>, args));
+    MPSBNB_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemv4_tc_kernel<XT, NB>, args));
     return check_launch();
+}
+// batch <= 16 runs the 16-column instance (half the x tile, more weight slots), 17 .. 32 the 32-column one
+template <typename XT>
+static int tc_launch(TcArgs &args, int grid, cudaStream_t st, bool pdl) {
+    return args.M <= 16 ? tc_launch_nb<XT, 16>(args, grid, st, pdl) : tc_launch_nb<XT, 32>(args, grid, st, pdl);
 }
 
 int tc_status_fetch(int *out, bool reset) {

@@ -175,9 +175,9 @@ class LayerStack:
             self._build_persistent_plan(M)
         elif M <= 8:
             self._build_plans(M)
-        elif M <= 16 and self.mid_batch_tcgen05:
-            # batch 9 .. 16: grouped launches of the tcgen05 decode kernel (its MMAs are N = 16 wide anyway), one per
-            # layer, with the boundary as its own kernel
+        elif M <= 32 and self.mid_batch_tcgen05:
+            # batch 9 .. 32: grouped launches of the tcgen05 decode kernel (its MMAs are 16 or 32 columns wide), one
+            # per layer, with the boundary as its own kernel
             lib = N.lib()
             old = lib.mpsbnb_decode_kernel_select(C.c_int(1))
             try:

@@ -362,6 +362,28 @@ def modules(ref_path):
     g["cfg_back_dtype"] = np.array(str(back.bnb_4bit_compute_dtype))
     g["cfg_method"] = np.array([cfg.quantization_method, ref.BitsAndBytesConfig(load_in_8bit=True).quantization_method,
                                 ref.BitsAndBytesConfig().quantization_method], dtype=str)
+    # ---- a Hugging Face model (random-init tiny Llama; no checkpoint is involved) through quantize_model
+    try:
+        from transformers import LlamaConfig, LlamaForCausalLM
+        hcfg = LlamaConfig(vocab_size=96, hidden_size=64, intermediate_size=128, num_hidden_layers=2,
+                           num_attention_heads=4, num_key_value_heads=2, max_position_embeddings=64)
+        torch.manual_seed(57)
+        hf = LlamaForCausalLM(hcfg).half().eval()
+        hids = torch.randint(0, 96, (2, 9))
+        g["hf_ids"] = hids.numpy()
+        g["hf_keys"] = np.array(list(hf.state_dict().keys()), dtype=str)
+        for k_, v_ in hf.state_dict().items():
+            g["hf_sd_" + k_] = v_.numpy()
+        with torch.no_grad():
+            h4 = ref.quantize_model(copy.deepcopy(hf), ref.BitsAndBytesConfig(load_in_4bit=True), device="cpu",
+                                    modules_to_not_convert=["lm_head"])
+            g["hf_y4"] = h4(hids).logits.numpy()
+            g["hf_n4"] = np.array(sum(type(m).__name__ == "Linear4bit" for m in h4.modules()))
+            h8 = ref.quantize_model(copy.deepcopy(hf), load_in_8bit=True, device="cpu")
+            g["hf_y8"] = h8(hids).logits.numpy()
+            g["hf_n8"] = np.array(sum(type(m).__name__ == "Linear8bit" for m in h8.modules()))
+    except ImportError:
+        print("transformers not importable: Hugging Face fixture skipped")
     # ---- checkpoints written by the reference
     torch.manual_seed(56)
     lin = torch.nn.Linear(128, 48).half()

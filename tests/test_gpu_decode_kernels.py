@@ -46,7 +46,7 @@ def test_default_kernel_both_types(M, dt):
 
 
 @pytest.mark.parametrize("dt", ["float16", "bfloat16"])
-@pytest.mark.parametrize("M", [1, 2, 5, 8, 9, 16])
+@pytest.mark.parametrize("M", [1, 2, 5, 8, 9, 16, 17, 25, 32])
 def test_tcgen05_kernel_matches_oracle(tcgen05_kernel, M, dt):
     rng = np.random.default_rng(200 + M)
     # one stage / many stages / ragged K and N / scale groups that are not 4-aligned (nb = 65) / 33 row tiles

@@ -108,3 +108,28 @@ def test_reference_checkpoints_load(golden):
     e4 = bnb.Embedding4bit(40, 128, device="cuda")
     e4.load_state_dict(torch.load(os.path.join(GOLDEN, "ref_embedding4bit.pt"), weights_only=False))
     assert np.array_equal(to_np(e4(torch.from_numpy(g["ck_eids"]).cuda())), g["ck_e4"])
+
+
+def test_quantize_model_on_a_hugging_face_llama(golden):
+    """A random-init two-layer LlamaForCausalLM (transformers) quantised by quantize_model gives the logits the
+    reference's quantize_model gives for the same weights (4-bit NF4 with lm_head skipped; 8-bit everywhere)."""
+    transformers = pytest.importorskip("transformers")
+    g = golden("modules")
+    if "hf_ids" not in g:
+        pytest.skip("fixture was generated without transformers")
+    cfg = transformers.LlamaConfig(vocab_size=96, hidden_size=64, intermediate_size=128, num_hidden_layers=2,
+                                   num_attention_heads=4, num_key_value_heads=2, max_position_embeddings=64)
+
+    def model():
+        m = transformers.LlamaForCausalLM(cfg).half().eval()
+        m.load_state_dict({k: torch.from_numpy(g["hf_sd_" + k]) for k in g["hf_keys"]})
+        return m
+    ids = torch.from_numpy(g["hf_ids"]).cuda()
+    with torch.no_grad():
+        m4 = bnb.quantize_model(model(), bnb.BitsAndBytesConfig(load_in_4bit=True), modules_to_not_convert=["lm_head"])
+        assert sum(isinstance(m, bnb.Linear4bit) for m in m4.modules()) == int(g["hf_n4"])
+        assert isinstance(m4.lm_head, torch.nn.Linear)
+        assert rel_err(to_np(m4(ids).logits), g["hf_y4"]) <= 1e-2
+        m8 = bnb.quantize_model(model(), load_in_8bit=True)
+        assert sum(isinstance(m, bnb.Linear8bit) for m in m8.modules()) == int(g["hf_n8"])
+        assert rel_err(to_np(m8(ids).logits), g["hf_y8"]) <= 1e-2
