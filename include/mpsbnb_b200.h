@@ -97,15 +97,18 @@ int mpsbnb_dequantize_blockwise(const int8_t *q, const float *absmax, int64_t n,
  * x, bias in x_dtype (F16 or BF16); y in y_dtype; fp32 accumulation.
  * ------------------------------------------------------------------------------------- */
 
-/* Decode shapes (M <= mpsbnb_gemv_4bit_max_m()): weights streamed once from HBM.
- * Needs blocksize 64 (any K; Kp/2 bytes per row).  No workspace. */
+/* Decode shapes (M <= mpsbnb_gemv_4bit_max_m() = 32): weights streamed once from HBM.
+ * Needs blocksize 64 (any K; Kp/2 bytes per row).  No workspace.
+ * M <= 8: TMA ring + table expansion + dot products / mma.sync; 9 <= M <= 32: TMA ring + expansion
+ * into tensor memory + tcgen05.mma (packed rows must be 16-byte aligned for both; otherwise, and
+ * for unaligned rows, a direct-load kernel). */
 int mpsbnb_gemv_4bit_max_m(void);
 int mpsbnb_gemv_4bit(const void *x, int x_dtype, int64_t M, const uint8_t *packed,
                      const void *absmax, const float *absmax2, int64_t N, int64_t K,
                      int blocksize, int quant_type, const void *bias, void *y, int y_dtype,
                      void *stream);
 
-/* Grouped decode GEMV: several 4-bit linears (block size 64, batch M <= 8) in ONE launch of
+/* Grouped decode GEMV: several 4-bit linears (block size 64, batch M <= mpsbnb_gemv_4bit_group_max_m()) in ONE launch of
  * a persistent kernel, e.g. the seven projections of a decoder layer.  Replaces a sequence
  * of _C.matmul_nf4 / _C.matmul_fp4 calls (mps_bitsandbytes.mm:2741-2751), which the
  * reference issues one Metal dispatch at a time.
@@ -133,12 +136,12 @@ typedef struct mpsbnb_linear4_desc {
 /* Two kernels implement the M <= 8 decode path.  0 (default): TMA ring, table expansion, dot
  * products (M <= 2) or mma.sync (M <= 8) in the consumer warps.  1: TMA ring, table expansion
  * into tensor memory, tcgen05.mma with fp32 accumulators in tensor memory, stream-K work split,
- * batch up to 16.
+ * batch up to 32 (a 16-column and a 32-column instance).
  * Selects the kernel used by later mpsbnb_gemv_4bit / mpsbnb_gemv_4bit_group_plan calls of this
  * process (other values: query only) and returns the previous selection.  The environment
  * variable MPSBNB_GEMV_IMPL=tc sets the initial value to 1.  No reference counterpart. */
 int mpsbnb_decode_kernel_select(int which);
-/* Largest batch M a group plan accepts with the kernel selected now (8; 16 for the tcgen05 kernel). */
+/* Largest batch M a group plan accepts with the kernel selected now (8; 32 for the tcgen05 kernel). */
 int mpsbnb_gemv_4bit_group_max_m(void);
 
 /* Optional closing step of a grouped launch, run inside the kernel by the CTA that finishes last (so no

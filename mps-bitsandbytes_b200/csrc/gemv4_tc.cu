@@ -1,4 +1,4 @@
-// Decode-shape (M <= 8) 4-bit linear on the Blackwell tensor path: y[M,N] = x[M,K] . dequant(W)[N,K]^T.
+// Decode-shape (M <= 32) 4-bit linear on the Blackwell tensor path: y[M,N] = x[M,K] . dequant(W)[N,K]^T.
 //
 // HBM-bound: the packed weights are read exactly once, by TMA, into a shared-memory ring; everything
 // else is arranged so that the ring never waits.  One persistent CTA per SM, warp-specialised:
@@ -6,14 +6,14 @@
 //   warp 16      TMA producer: one 16 KiB box (128 weight rows x 256 k, 128-byte swizzle) per stage.
 //   warps 18-19  loaders: per stage the 128 x 4 block scales (fp32, or int8 * second-level absmax / 127)
 //                and the 256 x values of every batch row, the latter written as the K-major, 128-byte
-//                swizzled B tile [16 x 256] that tcgen05.mma reads (rows >= M stay zero).
+//                swizzled B tile [NB x 256] that tcgen05.mma reads (NB = 16 or 32 batch columns; rows >= M stay zero).
 //   warps 0-15   expanders.  Warp (r, b) owns weight rows 32 r .. 32 r + 31 and block b of the stage: a lane
 //                reads the 32 packed bytes of ITS row, turns every byte into a (code, code) half2 with one
 //                byte-permute + one shared load (lane-replicated 256-entry table), multiplies by the block
 //                scale and stores the 64 fp16 weights with ONE tcgen05.st into the A tile in tensor memory
 //                (TMEM lane = weight row, 2 k per 32-bit column).  No mma.sync, no fragment shuffles.
-//   warp 17      one thread issues 16 tcgen05.mma (M = 128, N = 16, K = 16; A from TMEM, B = x from shared
-//                memory) per stage into an fp32 accumulator in TMEM and commits to mbarriers.
+//   warp 17      one thread issues 16 tcgen05.mma (M = 128, N = NB, K = 16; A from TMEM, B = x from shared
+//                memory) per stage into fp32 accumulators in TMEM and commits to mbarriers.
 //   warps 20-23  epilogue: when a row tile's K range is finished, read the accumulator (tcgen05.ld), add the
 //                bias, store y (or atomically add into an fp32 target).
 //
@@ -51,9 +51,10 @@ constexpr uint32_t TG_LUT_ABS = 131072u;                   // table at an absolu
 constexpr uint32_t TG_HIGH_ABS = TG_LUT_ABS + 65536u;      // entry b of lane l sits at b * 256 + l * 4: a 64 KiB span
 constexpr int TG_SMEM_BYTES = 227 * 1024;
 constexpr uint32_t TG_TMEM_COLS = 512, TG_D_COL0 = TG_ABUFS * 128;
-// Consecutive K steps add into tg_dsplit(NB) DIFFERENT accumulators (step j -> accumulator j % split), which
-// the epilogue sums: an MMA of this small shape is bound by the latency of its read-modify-write of the
-// accumulator, and MMAs on independent accumulators need not wait for each other.
+// Consecutive K steps add into tg_dsplit(NB) different accumulators (step j -> accumulator j % split), which
+// the epilogue sums.  (Measured: an MMA of this shape costs about 46 cycles whatever N <= 64 is and whether
+// or not consecutive MMAs share an accumulator, so the split neither helps nor hurts; it keeps the fp32
+// partial sums of a long K shorter.)
 // (two accumulator buffers of NB * split columns each fit the 128 columns left beside the A tiles.)
 __host__ __device__ constexpr int tg_dsplit(int nb) { return 64 / nb; }
 static_assert(TG_NXS % TG_LOADERS == 0, "each scale/x slot must belong to exactly one loader warp");
