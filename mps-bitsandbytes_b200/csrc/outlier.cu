@@ -64,6 +64,34 @@ __global__ void __launch_bounds__(256) outlier_w_kernel(const int8_t *__restrict
     }
 }
 
+// The same, 16 elements per thread (K % 16 == 0, 16-byte aligned rows): one 16-byte load of codes, four of
+// the column map, two 16-byte stores.  Bound by HBM instead of by the per-element index arithmetic.
+template <typename T>
+__global__ void __launch_bounds__(256) outlier_w16_kernel(const int8_t *__restrict__ q, const float *__restrict__ scales,
+                                                          const T *__restrict__ outlier_w, int64_t n_out, int64_t N,
+                                                          int64_t K, const int *__restrict__ slot, T *__restrict__ out,
+                                                          int64_t ld) {
+    const int64_t cpr = K / 16, total = N * cpr;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        int64_t n, c;
+        if (total < 0x7fffffffll) { const uint32_t n32 = (uint32_t)i / (uint32_t)cpr; n = n32; c = (uint32_t)i - n32 * (uint32_t)cpr; }
+        else { n = i / cpr; c = i - n * cpr; }
+        const uint4 w = __ldg(reinterpret_cast<const uint4 *>(q + n * K + c * 16));
+        const int8_t *b = reinterpret_cast<const int8_t *>(&w);
+        __align__(16) int sl[16];
+#pragma unroll
+        for (int v = 0; v < 4; ++v) reinterpret_cast<int4 *>(sl)[v] = __ldg(reinterpret_cast<const int4 *>(slot + c * 16) + v);
+        const float s127 = __fdiv_rn(__ldg(scales + n), 127.0f);
+        __align__(16) T vals[16];
+#pragma unroll
+        for (int e = 0; e < 16; ++e)
+            vals[e] = sl[e] == 0 ? i8_times_rounded_scale<T>(b[e], s127) : outlier_w[n * n_out + (sl[e] - 1)];
+        uint4 *dst = reinterpret_cast<uint4 *>(out + n * ld + c * 16);
+        dst[0] = reinterpret_cast<const uint4 *>(vals)[0];
+        dst[1] = reinterpret_cast<const uint4 *>(vals)[1];
+    }
+}
+
 static inline unsigned o_grid(int64_t items) {
     const int64_t ctas = (items + 255) / 256, cap = (int64_t)sm_count() * 16;
     return (unsigned)(ctas < 1 ? 1 : (ctas > cap ? cap : ctas));
@@ -103,13 +131,16 @@ extern "C" int mpsbnb_outlier_linear(const void *x, int x_dtype, int64_t M, cons
         int rc = check_launch();
         if (rc != MPSBNB_OK) return rc;
     }
+    const bool vec16 = K % 16 == 0 && aligned16(W);             // slot and the operand live in the 256-byte aligned workspace
     const unsigned xgrid = (unsigned)(M < (int64_t)sm_count() * 8 ? M : (int64_t)sm_count() * 8);
     if (op_dtype == MPSBNB_F16) {
         MPSBNB_DISPATCH_DTYPE(x_dtype, TX, (outlier_x_kernel<TX, __half><<<xgrid, 256, 0, st>>>((const TX *)x, M, K, slot, (__half *)xo, ld)));
-        outlier_w_kernel<__half><<<o_grid(N * K), 256, 0, st>>>(W, w_scales, (const __half *)outlier_w, n_outliers, N, K, slot, (__half *)wo, ld);
+        if (vec16) outlier_w16_kernel<__half><<<o_grid(N * K / 16), 256, 0, st>>>(W, w_scales, (const __half *)outlier_w, n_outliers, N, K, slot, (__half *)wo, ld);
+        else outlier_w_kernel<__half><<<o_grid(N * K), 256, 0, st>>>(W, w_scales, (const __half *)outlier_w, n_outliers, N, K, slot, (__half *)wo, ld);
     } else {
         MPSBNB_DISPATCH_DTYPE(x_dtype, TX, (outlier_x_kernel<TX, __nv_bfloat16><<<xgrid, 256, 0, st>>>((const TX *)x, M, K, slot, (__nv_bfloat16 *)xo, ld)));
-        outlier_w_kernel<__nv_bfloat16><<<o_grid(N * K), 256, 0, st>>>(W, w_scales, (const __nv_bfloat16 *)outlier_w, n_outliers, N, K, slot, (__nv_bfloat16 *)wo, ld);
+        if (vec16) outlier_w16_kernel<__nv_bfloat16><<<o_grid(N * K / 16), 256, 0, st>>>(W, w_scales, (const __nv_bfloat16 *)outlier_w, n_outliers, N, K, slot, (__nv_bfloat16 *)wo, ld);
+        else outlier_w_kernel<__nv_bfloat16><<<o_grid(N * K), 256, 0, st>>>(W, w_scales, (const __nv_bfloat16 *)outlier_w, n_outliers, N, K, slot, (__nv_bfloat16 *)wo, ld);
     }
     int rc = check_launch();
     if (rc != MPSBNB_OK) return rc;

@@ -156,6 +156,53 @@ __global__ void dequantize_fp8_kernel(const uint8_t *__restrict__ codes, const f
         }
 }
 
+// Operand expansion for the GEMM paths, 16 elements per thread: one 16-byte load, two 16-byte stores (fp32
+// output: four).  Needs cols % 16 == 0, a 16-byte aligned source and destination and ld % 8 == 0.  The
+// one-element kernels above spend their time on a 64-bit division per element; this one is bound by HBM.
+// KIND 0: int8 * (row / 127); 2: int8 * (sqrt(row * col) / 127); 3: FP8 E4M3 code * row scale.
+template <typename T, int KIND>
+__global__ void __launch_bounds__(256) expand16_kernel(const uint8_t *__restrict__ src, int64_t rows, int64_t cols,
+                                                       const float *__restrict__ row_s, const float *__restrict__ col_s,
+                                                       T *__restrict__ out, int64_t ld) {
+    __shared__ float lut[256];
+    if (KIND == 3) {
+        for (int i = threadIdx.x; i < 256; i += blockDim.x) lut[i] = fp8_decode(i);
+        __syncthreads();
+    }
+    const int64_t cpr = cols / 16, total = rows * cpr;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        int64_t r, c;
+        if (total < 0x7fffffffll) { const uint32_t r32 = (uint32_t)i / (uint32_t)cpr; r = r32; c = (uint32_t)i - r32 * (uint32_t)cpr; }
+        else { r = i / cpr; c = i - r * cpr; }
+        const uint4 w = __ldg(reinterpret_cast<const uint4 *>(src + r * cols + c * 16));
+        const uint8_t *b = reinterpret_cast<const uint8_t *>(&w);
+        const float rs = __ldg(row_s + r);
+        __align__(16) T vals[16];
+        if (KIND == 0) {
+            const float f = __fdiv_rn(rs, 127.0f);
+#pragma unroll
+            for (int e = 0; e < 16; ++e) vals[e] = from_f32<T>(__fmul_rn((float)(int8_t)b[e], f));
+        } else if (KIND == 2) {
+            __align__(16) float cs[16];
+#pragma unroll
+            for (int v = 0; v < 4; ++v) reinterpret_cast<float4 *>(cs)[v] = __ldg(reinterpret_cast<const float4 *>(col_s + c * 16) + v);
+#pragma unroll
+            for (int e = 0; e < 16; ++e)
+                vals[e] = from_f32<T>(__fmul_rn((float)(int8_t)b[e], __fdiv_rn(__fsqrt_rn(__fmul_rn(rs, cs[e])), 127.0f)));
+        } else {
+#pragma unroll
+            for (int e = 0; e < 16; ++e) vals[e] = from_f32<T>(__fmul_rn(lut[b[e]], rs));
+        }
+        uint4 *dst = reinterpret_cast<uint4 *>(out + r * ld + c * 16);
+#pragma unroll
+        for (int v = 0; v < (int)sizeof(T); ++v) dst[v] = reinterpret_cast<const uint4 *>(vals)[v];
+    }
+}
+
+static inline bool expand16_ok(const void *src, int64_t cols, const void *out, int64_t ld, const void *col_s) {
+    return cols % 16 == 0 && ld % 8 == 0 && aligned16(src) && aligned16(out) && (col_s == nullptr || aligned16(col_s));
+}
+
 static int grid_1d(int64_t n, int threads = 256) {
     int64_t g = (n + threads - 1) / threads;
     const int64_t cap = (int64_t)sm_count() * 16;
@@ -192,6 +239,37 @@ __global__ void dequantize_i8_transposed_kernel(const int8_t *__restrict__ B, co
     }
 }
 
+// The same through a 64 x 64 tile: 16-byte loads along n, 16-byte stores along k (16-bit output only).
+// Needs N % 16 == 0, K % 8 == 0, B and out 16-byte aligned, ld % 8 == 0.
+template <typename T>
+__global__ void __launch_bounds__(256) dequantize_i8_transposed64_kernel(const int8_t *__restrict__ B, const float *__restrict__ col_s,
+                                                                         int64_t K, int64_t N, T *__restrict__ out, int64_t ld) {
+    static_assert(sizeof(T) == 2, "16-bit output");
+    __shared__ __align__(16) int8_t tile[64][80];               // pitch 80: rows stay 16-byte aligned
+    const int64_t k0 = (int64_t)blockIdx.y * 64, n0 = (int64_t)blockIdx.x * 64;
+    const int t = threadIdx.x;
+    {
+        const int kr = t >> 2, nc = (t & 3) * 16;               // 64 rows x 4 chunks of 16 columns
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (k0 + kr < K && n0 + nc < N) v = __ldg(reinterpret_cast<const uint4 *>(B + (k0 + kr) * N + n0 + nc));
+        *reinterpret_cast<uint4 *>(&tile[kr][nc]) = v;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+        const int id = t + 256 * j;                             // 64 columns x 8 chunks of 8 k
+        const int nn = id >> 3, kc = (id & 7) * 8;
+        const int64_t n = n0 + nn, k = k0 + kc;
+        if (n < N && k < K) {
+            const float f = __fdiv_rn(__ldg(col_s + n), 127.0f);
+            __align__(16) T vals[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) vals[e] = from_f32<T>(__fmul_rn((float)tile[kc + e][nn], f));
+            *reinterpret_cast<uint4 *>(out + n * ld + k) = *reinterpret_cast<const uint4 *>(vals);
+        }
+    }
+}
+
 template <typename T>
 __global__ void copy_rows_kernel(const T *__restrict__ src, int64_t rows, int64_t cols, T *__restrict__ dst, int64_t ld) {
     const int64_t total = rows * cols;
@@ -203,6 +281,14 @@ __global__ void copy_rows_kernel(const T *__restrict__ src, int64_t rows, int64_
 
 int dequantize_i8_ld(const int8_t *q, int64_t rows, int64_t cols, const float *row_s, const float *col_s, void *out,
                      int64_t ld, int out_dtype, cudaStream_t st) {
+    if (expand16_ok(q, cols, out, ld, col_s)) {
+        const uint8_t *src = reinterpret_cast<const uint8_t *>(q);
+        if (col_s == nullptr)
+            MPSBNB_DISPATCH_DTYPE(out_dtype, T, (expand16_kernel<T, 0><<<grid_1d(rows * cols / 16), 256, 0, st>>>(src, rows, cols, row_s, nullptr, (T *)out, ld)));
+        else
+            MPSBNB_DISPATCH_DTYPE(out_dtype, T, (expand16_kernel<T, 2><<<grid_1d(rows * cols / 16), 256, 0, st>>>(src, rows, cols, row_s, col_s, (T *)out, ld)));
+        return check_launch();
+    }
     if (col_s == nullptr)
         MPSBNB_DISPATCH_DTYPE(out_dtype, T, (dequantize_i8_kernel<T, 0><<<grid_1d(rows * cols), 256, 0, st>>>(
                                                 q, rows, cols, row_s, nullptr, (T *)out, ld)));
@@ -214,6 +300,12 @@ int dequantize_i8_ld(const int8_t *q, int64_t rows, int64_t cols, const float *r
 
 int dequantize_i8_transposed_ld(const int8_t *B, const float *col_s, int64_t K, int64_t N, void *out, int64_t ld,
                                 int out_dtype, cudaStream_t st) {
+    if (is_16bit(out_dtype) && N % 16 == 0 && K % 8 == 0 && ld % 8 == 0 && aligned16(B) && aligned16(out)) {
+        const dim3 grid64((unsigned)((N + 63) / 64), (unsigned)((K + 63) / 64));
+        if (out_dtype == MPSBNB_F16) dequantize_i8_transposed64_kernel<__half><<<grid64, 256, 0, st>>>(B, col_s, K, N, (__half *)out, ld);
+        else dequantize_i8_transposed64_kernel<__nv_bfloat16><<<grid64, 256, 0, st>>>(B, col_s, K, N, (__nv_bfloat16 *)out, ld);
+        return check_launch();
+    }
     const dim3 grid((unsigned)((N + 31) / 32), (unsigned)((K + 31) / 32)), block(32, 8);
     MPSBNB_DISPATCH_DTYPE(out_dtype, T, (dequantize_i8_transposed_kernel<T><<<grid, block, 0, st>>>(B, col_s, K, N, (T *)out, ld)));
     return check_launch();
@@ -221,6 +313,10 @@ int dequantize_i8_transposed_ld(const int8_t *B, const float *col_s, int64_t K, 
 
 int dequantize_fp8_ld(const uint8_t *codes, const float *scales, int64_t rows, int64_t cols, void *out, int64_t ld,
                       int out_dtype, cudaStream_t st) {
+    if (expand16_ok(codes, cols, out, ld, nullptr)) {
+        MPSBNB_DISPATCH_DTYPE(out_dtype, T, (expand16_kernel<T, 3><<<grid_1d(rows * cols / 16), 256, 0, st>>>(codes, rows, cols, scales, nullptr, (T *)out, ld)));
+        return check_launch();
+    }
     MPSBNB_DISPATCH_DTYPE(out_dtype, T, (dequantize_fp8_kernel<T><<<grid_1d(rows * cols), 256, 0, st>>>(
                                             codes, scales, rows, cols, (T *)out, ld)));
     return check_launch();
