@@ -7,11 +7,13 @@
 //   warps 18-19  loaders: per stage the 128 x 4 block scales (fp32, or int8 * second-level absmax / 127)
 //                and the 256 x values of every batch row, the latter written as the K-major, 128-byte
 //                swizzled B tile [NB x 256] that tcgen05.mma reads (NB = 16 or 32 batch columns; rows >= M stay zero).
-//   warps 0-15   expanders.  Warp (r, b) owns weight rows 32 r .. 32 r + 31 and block b of the stage: a lane
-//                reads the 32 packed bytes of ITS row, turns every byte into a (code, code) half2 with one
-//                byte-permute + one shared load (lane-replicated 256-entry table), multiplies by the block
-//                scale and stores the 64 fp16 weights with ONE tcgen05.st into the A tile in tensor memory
-//                (TMEM lane = weight row, 2 k per 32-bit column).  No mma.sync, no fragment shuffles.
+//   warps 0-15   expanders, in two groups of eight that take alternate stages (a warp passes the barriers once
+//                per two stages; the groups overlap).  In a group, warp (h, r) owns weight rows 32 r .. 32 r + 31
+//                and blocks 2 h, 2 h + 1 of the stage: a lane reads the 64 packed bytes of ITS row, turns every
+//                byte into a (code, code) half2 with one byte-permute + one shared load (lane-replicated
+//                256-entry table), multiplies by the block scale and stores the 2 x 64 fp16 weights with two
+//                tcgen05.st into the A tile in tensor memory (TMEM lane = weight row, 2 k per 32-bit column).
+//                No mma.sync, no fragment shuffles.
 //   warp 17      one thread issues 16 tcgen05.mma (M = 128, N = NB, K = 16; A from TMEM, B = x from shared
 //                memory) per stage into fp32 accumulators in TMEM and commits to mbarriers.
 //   warps 20-23  epilogue: when a row tile's K range is finished, read the accumulator (tcgen05.ld), add the
@@ -36,6 +38,8 @@ namespace mpsbnb {
 using namespace sm100;
 
 constexpr int TG_CONSUMERS = 16;
+constexpr int TG_EGROUPS = 2;                              // expander groups (of TG_CONSUMERS / TG_EGROUPS warps) that alternate stages
+constexpr int TG_GROUP_WARPS = TG_CONSUMERS / TG_EGROUPS;
 constexpr int TG_WARP_PRODUCER = 16, TG_WARP_MMA = 17, TG_WARP_LOADER0 = 18, TG_LOADERS = 2, TG_WARP_EPI0 = 20;
 constexpr int TG_THREADS = 24 * 32;
 constexpr int TG_ROWS = 128;                               // weight rows per tile = UMMA M
@@ -180,9 +184,9 @@ __global__ void __launch_bounds__(TG_THREADS, 1) gemv4_tc_kernel(const __grid_co
     pdl_launch_dependents();
 
     if (tid == 0) {
-        for (int s = 0; s < nslots; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), TG_CONSUMERS); }
-        for (int s = 0; s < TG_NXS; ++s) { mbar_init(xfull_bar(s), 32); mbar_init(xempty_bar(s), TG_CONSUMERS + 1); }
-        for (int s = 0; s < TG_ABUFS; ++s) { mbar_init(afull_bar(s), TG_CONSUMERS); mbar_init(aempty_bar(s), 1); }
+        for (int s = 0; s < nslots; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), TG_GROUP_WARPS); }
+        for (int s = 0; s < TG_NXS; ++s) { mbar_init(xfull_bar(s), 32); mbar_init(xempty_bar(s), TG_GROUP_WARPS + 1); }
+        for (int s = 0; s < TG_ABUFS; ++s) { mbar_init(afull_bar(s), TG_GROUP_WARPS); mbar_init(aempty_bar(s), 1); }
         for (int s = 0; s < 2; ++s) { mbar_init(dfull_bar(s), 1); mbar_init(dempty_bar(s), 4); }
         *abort_flag = 0;
         fence_mbar_init();
@@ -513,71 +517,73 @@ __global__ void __launch_bounds__(TG_THREADS, 1) gemv4_tc_kernel(const __grid_co
         }
     } else {
         // ------------------------------------------------------------ expanders: packed bytes -> fp16 weights in TMEM
-        const int r = warp & 3, b = warp >> 2;                           // TMEM lane quarter, block of the stage
+        // Two groups of eight warps; group g takes the stages q = g, g + 2, ... of the CTA's sequence, so a warp
+        // goes through the barriers once per TWO stages and the groups overlap each other.  Inside a group warp
+        // (h, r) owns weight rows 32 r .. 32 r + 31 and the blocks 2 h, 2 h + 1 of the stage.
+        const int g = warp >> 3, h = (warp >> 2) & 1, r = warp & 3;
         const int row = 32 * r + lane;
-        const uint32_t woff0 = (uint32_t)(row * 128 + (((2 * b) ^ (row & 7)) << 4));
-        const uint32_t woff1 = (uint32_t)(row * 128 + (((2 * b + 1) ^ (row & 7)) << 4));
         const uint32_t lane_word = TG_LUT_ABS | ((uint32_t)lane * 4u);   // bytes 0, 2, 3 of every table address
-        const uint32_t tmem_mine = tmem_base + ((uint32_t)(32 * r) << 16) + (uint32_t)(32 * b);
-        int slot = 0, xslot = 0, abuf = 0;
-        uint32_t ph = 0, xph = 0, aph = 0;
-        bool ok = true;
-        // total number of stages of this CTA
-        int total = 0;
-        for (int p = p_first; p < p_last; p += p_step) { const TcPiece pc = piece_of(p); total += pc.s_end - pc.s_begin; }
-        // waits for the next stage in the weight ring, pulls this lane's 32 bytes, frees the slot
-        auto fetch = [&](uint4 &lo, uint4 &hi) {
-            if (!mbar_wait_sleep(full_bar(slot), ph, abort_flag, kSleepFast)) { atomicExch(&g_tc_status, 407); *abort_flag = 1; ok = false; return; }
-            const uint32_t sb = sm.addr(slot);
-            lo = tg_lds128(sb + woff0);
-            hi = tg_lds128(sb + woff1);
-            const uint32_t dep = hi.w & a.zero;                          // the arrive cannot issue before the loads returned
-            __syncwarp();
-            if (lane == 0) mbar_arrive(empty_bar(slot) + dep);
-            if (++slot == nslots) { slot = 0; ph ^= 1u; }
-        };
-        auto expand = [&](const uint4 &lo, const uint4 &hi) {
-            if (!mbar_wait_sleep(xfull_bar(xslot), xph, abort_flag, kSleepFast)) { atomicExch(&g_tc_status, 408); *abort_flag = 1; ok = false; return; }
-            // my (row, block) scale: fp32 [row][4], or int8 codes [row] + second-level maximum [row]
-            const uint32_t ab = s_xs + (uint32_t)(xslot * XS_BYTES) + X_BYTES;
-            float scale;
-            if (tg_lds_u32(s_mode + 4u * xslot) != 0u) {
-                const int code = (int)(int8_t)((tg_lds_u32(ab + (uint32_t)(row * 4)) >> (8 * b)) & 0xFFu);
-                scale = (float)code * __fdiv_rn(tg_lds_f32(ab + 512u + (uint32_t)(row * 4)), 127.0f);
-            } else {
-                scale = tg_lds_f32(ab + (uint32_t)(row * 16 + b * 4));
-            }
-            const uint32_t s2 = tg_pair_bits<XT>(scale, scale);
-            const uint32_t wv[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
-            uint32_t out[32];
+        const uint32_t tmem_mine = tmem_base + ((uint32_t)(32 * r) << 16) + (uint32_t)(64 * h);
+        uint32_t woff[4];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                out[4 * i + 0] = tg_mul2<XT>(tg_lut(__byte_perm(wv[i], lane_word, 0x7604)), s2);
-                out[4 * i + 1] = tg_mul2<XT>(tg_lut(__byte_perm(wv[i], lane_word, 0x7614)), s2);
-                out[4 * i + 2] = tg_mul2<XT>(tg_lut(__byte_perm(wv[i], lane_word, 0x7624)), s2);
-                out[4 * i + 3] = tg_mul2<XT>(tg_lut(__byte_perm(wv[i], lane_word, 0x7634)), s2);
+        for (int c = 0; c < 4; ++c) woff[c] = (uint32_t)(row * 128 + (((4 * h + c) ^ (row & 7)) << 4));
+        // ring positions of stage q = g: every ring is entered at position g and advanced by TG_EGROUPS per stage
+        int slot = g % nslots, xslot = g % TG_NXS, abuf = g % TG_ABUFS;
+        uint32_t ph = (uint32_t)(g / nslots) & 1u, xph = (uint32_t)(g / TG_NXS) & 1u, aph = (uint32_t)(g / TG_ABUFS) & 1u;
+        bool ok = true;
+        int total = 0;                                                   // stages of this CTA
+        for (int p = p_first; p < p_last; p += p_step) { const TcPiece pc = piece_of(p); total += pc.s_end - pc.s_begin; }
+        for (int q = g; q < total && ok && !*abort_flag; q += TG_EGROUPS) {
+            // the stage's packed bytes: this lane's 64 bytes, then the slot is free for the producer
+            if (!mbar_wait_sleep(full_bar(slot), ph, abort_flag, kSleepFast)) { atomicExch(&g_tc_status, 407); *abort_flag = 1; ok = false; break; }
+            const uint32_t sb = sm.addr(slot);
+            uint4 w4[4];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) w4[c] = tg_lds128(sb + woff[c]);
+            {
+                const uint32_t dep = w4[3].w & a.zero;                   // the arrive cannot issue before the loads returned
+                __syncwarp();
+                if (lane == 0) mbar_arrive(empty_bar(slot) + dep);
             }
-            // the A tile is free once the MMAs that read it three stages ago have completed
-            if (!mbar_wait_sleep(aempty_bar(abuf), aph ^ 1u, abort_flag, kSleepFast)) { atomicExch(&g_tc_status, 409); *abort_flag = 1; ok = false; return; }
-            tc_fence_after();
-            tmem_st_32x32(tmem_mine + (uint32_t)(abuf * 128), out);
+            if (!mbar_wait_sleep(xfull_bar(xslot), xph, abort_flag, kSleepFast)) { atomicExch(&g_tc_status, 408); *abort_flag = 1; ok = false; break; }
+            const uint32_t ab = s_xs + (uint32_t)(xslot * XS_BYTES) + X_BYTES;
+            const bool coded = tg_lds_u32(s_mode + 4u * xslot) != 0u;   // int8 codes [row] + second-level maximum [row], or fp32 [row][4]
+            const uint32_t codes = coded ? tg_lds_u32(ab + (uint32_t)(row * 4)) : 0u;
+            const float f2 = coded ? __fdiv_rn(tg_lds_f32(ab + 512u + (uint32_t)(row * 4)), 127.0f) : 0.0f;
+#pragma unroll
+            for (int bb = 0; bb < 2; ++bb) {
+                const int blk = 2 * h + bb;
+                const float scale = coded ? (float)(int)(int8_t)((codes >> (8 * blk)) & 0xFFu) * f2
+                                          : tg_lds_f32(ab + (uint32_t)(row * 16 + blk * 4));
+                const uint32_t s2 = tg_pair_bits<XT>(scale, scale);
+                const uint32_t wv[8] = {w4[2 * bb].x, w4[2 * bb].y, w4[2 * bb].z, w4[2 * bb].w,
+                                        w4[2 * bb + 1].x, w4[2 * bb + 1].y, w4[2 * bb + 1].z, w4[2 * bb + 1].w};
+                uint32_t out[32];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    out[4 * i + 0] = tg_mul2<XT>(tg_lut(__byte_perm(wv[i], lane_word, 0x7604)), s2);
+                    out[4 * i + 1] = tg_mul2<XT>(tg_lut(__byte_perm(wv[i], lane_word, 0x7614)), s2);
+                    out[4 * i + 2] = tg_mul2<XT>(tg_lut(__byte_perm(wv[i], lane_word, 0x7624)), s2);
+                    out[4 * i + 3] = tg_mul2<XT>(tg_lut(__byte_perm(wv[i], lane_word, 0x7634)), s2);
+                }
+                if (bb == 0) {
+                    // the A tile is free once the MMAs that read it three stages ago have completed
+                    if (!mbar_wait_sleep(aempty_bar(abuf), aph ^ 1u, abort_flag, kSleepFast)) { atomicExch(&g_tc_status, 409); *abort_flag = 1; ok = false; break; }
+                    tc_fence_after();
+                }
+                tmem_st_32x32(tmem_mine + (uint32_t)(abuf * 128 + 32 * bb), out);
+            }
+            if (!ok) break;
             tmem_st_wait();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) { mbar_arrive(afull_bar(abuf)); mbar_arrive(xempty_bar(xslot)); }
-            if (++abuf == TG_ABUFS) { abuf = 0; aph ^= 1u; }
-            if (++xslot == TG_NXS) { xslot = 0; xph ^= 1u; }
-        };
-        uint4 loA, hiA, loB, hiB;
-        if (total > 0) fetch(loA, hiA);
-        for (int q = 0; q < total && ok && !*abort_flag; q += 2) {
-            if (q + 1 < total) fetch(loB, hiB);
-            if (!ok) break;
-            expand(loA, hiA);
-            if (!(ok && q + 1 < total)) break;
-            if (q + 2 < total) fetch(loA, hiA);
-            if (!ok) break;
-            expand(loB, hiB);
+#pragma unroll
+            for (int e = 0; e < TG_EGROUPS; ++e) {
+                if (++slot == nslots) { slot = 0; ph ^= 1u; }
+                if (++xslot == TG_NXS) { xslot = 0; xph ^= 1u; }
+                if (++abuf == TG_ABUFS) { abuf = 0; aph ^= 1u; }
+            }
         }
     }
     // After a time-out the roles leave early while copies or MMAs may still be in flight: give them a
