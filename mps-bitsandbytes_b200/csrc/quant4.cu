@@ -70,6 +70,28 @@ template <int QT> __device__ __forceinline__ uint32_t code_of(float v) {
     return QT == MPSBNB_NF4 ? nf4_code(v) : fp4_code(v);
 }
 
+// NF4 search by buckets: [-1, 1] is cut into sixteen buckets of width 1/8; no bucket holds more than two of the
+// fifteen thresholds, so the code is (thresholds below the bucket) + (v > first) + (v > second): one FMA, one
+// conversion, one 8-byte shared load and two compares instead of four dependent compare-and-select levels.  The same
+// thresholds decide, so the result is the binary search's; the bucket a value within rounding error of an edge lands
+// in does not matter, because no threshold is closer than 1.7e-3 to an edge (oracle/oracle.c:o_prove_nf4_buckets
+// checks every float).  tab[g] = the bucket's two thresholds (+inf where it has fewer).
+#define NF4_INF __int_as_float(0x7f800000)
+__device__ __forceinline__ void nf4_bucket_table_fill(float2 *tab, int g) {
+    const float a[16] = {NF4_INF, NF4_T0, NF4_INF, NF4_T1, NF4_T2, NF4_T3, NF4_T4, NF4_T6, NF4_T7, NF4_T9, NF4_T10, NF4_T11, NF4_T12, NF4_T13, NF4_T14, NF4_INF};
+    tab[g] = make_float2(a[g], g == 6 ? NF4_T5 : (g == 8 ? NF4_T8 : NF4_INF));
+}
+__device__ __forceinline__ uint32_t nf4_code_bucket(float v, const float2 *tab) {
+    const int g = max(0, min(15, __float2int_rz(__fmaf_rn(v, 8.0f, 8.0f))));
+    const float2 t = tab[g];
+    // thresholds below bucket g, four bits each: 0 0 1 1 2 3 4 6 7 9 10 11 12 13 14 15
+    const uint32_t base = (uint32_t)(0xFEDCBA9764321100ull >> (4 * g)) & 15u;
+    return base + (v > t.x ? 1u : 0u) + (v > t.y ? 1u : 0u);
+}
+template <int QT> __device__ __forceinline__ uint32_t code_fast(float v, const float2 *tab) {
+    return QT == MPSBNB_NF4 ? nf4_code_bucket(v, tab) : fp4_code(v);
+}
+
 // x / a rounded to nearest, a > 0.  EXACT16: x and a are fp16- or bf16-representable and
 // 1e-30 <= a <= 1e30, where the 4-operation form is proven equal to IEEE division for
 // the purpose of code selection.
@@ -90,6 +112,11 @@ quantize4_fast_kernel(const T *__restrict__ A, int64_t rows, int64_t cols, int64
                       const float *__restrict__ absmax_in, uint8_t *__restrict__ packed,
                       float *__restrict__ absmax_out) {
     static_assert(sizeof(T) == 2, "fast path takes 16-bit input");
+    __shared__ float2 nf4_tab[16];
+    if (QT == MPSBNB_NF4) {
+        if (threadIdx.x < 16) nf4_bucket_table_fill(nf4_tab, threadIdx.x);
+        __syncthreads();
+    }
     constexpr int U = 4;                                   // 16-byte loads in flight per thread: the kernel is a
                                                            // pure stream and needs ~100 KB in flight per SM
     const int64_t total = rows * chunks_per_row;           // multiple of LPB
@@ -149,10 +176,10 @@ quantize4_fast_kernel(const T *__restrict__ A, int64_t rows, int64_t cols, int64
             if (a >= 1e-30f && a <= 1e30f && absmax_in == nullptr) {   // range covered by the proof
                 const float r = __frcp_rn(a);
 #pragma unroll
-                for (int j = 0; j < 8; ++j) word |= code_of<QT>(block_div<true>(x[j], a, r)) << (4 * j);
+                for (int j = 0; j < 8; ++j) word |= code_fast<QT>(block_div<true>(x[j], a, r), nf4_tab) << (4 * j);
             } else {
 #pragma unroll
-                for (int j = 0; j < 8; ++j) word |= code_of<QT>(block_div<false>(x[j], a, 0.f)) << (4 * j);
+                for (int j = 0; j < 8; ++j) word |= code_fast<QT>(block_div<false>(x[j], a, 0.f), nf4_tab) << (4 * j);
             }
             if (live) reinterpret_cast<uint32_t *>(packed)[cs[u]] = word;   // byte j/2: low nibble = even k
         }

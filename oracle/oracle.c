@@ -238,3 +238,30 @@ int64_t o_prove_thresholds(int qt, int window, int64_t n_random) {
     }
     return bad;
 }
+
+/* The bucket form of the NF4 search used by the fast CUDA quantiser: g = trunc(fma(v, 8, 8)) clamped to 0..15,
+ * code = (thresholds below bucket g) + (v > first threshold of g) + (v > second).  Compared with the plain
+ * threshold search on EVERY float whose ordered key is a multiple of `stride` (stride 1: all 2^32 bit patterns
+ * except NaN, values outside [-1, 1] included); returns the number of disagreements. */
+int64_t o_prove_nf4_buckets(int64_t stride) {
+    float t[15];
+    o_nf4_thresholds(t);
+    const float inf = INFINITY;
+    const float ta[16] = {inf, t[0], inf, t[1], t[2], t[3], t[4], t[6], t[7], t[9], t[10], t[11], t[12], t[13], t[14], inf};
+    float tb[16];
+    for (int g = 0; g < 16; ++g) tb[g] = inf;
+    tb[6] = t[5]; tb[8] = t[8];
+    const uint64_t base = 0xFEDCBA9764321100ull;
+    int64_t bad = 0;
+#pragma omp parallel for schedule(static) reduction(+ : bad)
+    for (int64_t k = 0; k < 0x100000000ll; k += stride) {
+        const float v = unord((uint32_t)k);
+        if (isnan(v)) continue;
+        const float f = fmaf(v, 8.0f, 8.0f);
+        int g = f >= 2147483648.0f ? 2147483647 : (f <= -2147483648.0f ? (-2147483647 - 1) : (int)f);   /* cvt.rzi.s32.f32 saturates */
+        g = g < 0 ? 0 : (g > 15 ? 15 : g);
+        const int got = (int)((base >> (4 * g)) & 15u) + (v > ta[g]) + (v > tb[g]);
+        bad += (got != o_nearest_by_threshold(v, 0, t));
+    }
+    return bad;
+}

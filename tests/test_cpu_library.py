@@ -2,6 +2,7 @@
 thresholds compiled into the CUDA quantiser are the ones the oracle derives, the shortcuts of
 the quantiser are proven against the reference arithmetic, and the Python surface mirrors
 the reference's names and argument order.  No kernel runs here."""
+import ctypes as C
 import inspect
 import os
 import re
@@ -48,6 +49,14 @@ def test_compiled_thresholds_match_oracle():
 @pytest.mark.parametrize("qt", [0, 1])
 def test_threshold_search_equals_16_way_search(qt):
     assert oracle_c.lib().o_prove_thresholds(qt, 2048, 2_000_000) == 0
+
+
+def test_nf4_bucket_search_equals_threshold_search():
+    """The fast quantiser's NF4 search (bucket by trunc(fma(v, 8, 8)), two compares) against the threshold search
+    on every third float bit pattern, values outside [-1, 1] included (stride 1, every float, also returns 0)."""
+    fn = oracle_c.lib().o_prove_nf4_buckets
+    fn.restype = C.c_int64
+    assert fn(C.c_int64(3)) == 0
 
 
 @pytest.mark.parametrize("qt,bf16", [(0, 0), (1, 0), (0, 1), (1, 1)])
