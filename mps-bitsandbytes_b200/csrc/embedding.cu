@@ -34,7 +34,9 @@ __global__ void __launch_bounds__(256) embedding4_vec_kernel(const void *__restr
     const int64_t chunks = D / 16;
     const int64_t total = n_idx * chunks;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-        const int64_t t = i / chunks, c = i - t * chunks;
+        int64_t t, c;                                              // 32-bit division where the sizes allow it
+        if (total < 0x7fffffffll) { const uint32_t t32 = (uint32_t)i / (uint32_t)chunks; t = t32; c = (uint32_t)i - t32 * (uint32_t)chunks; }
+        else { t = i / chunks; c = i - t * chunks; }
         const int64_t row = load_index(idx, idx64, t);
         __align__(16) T vals[16];
         if (row < 0 || row >= V || row == padding_idx) {
@@ -86,7 +88,9 @@ __global__ void __launch_bounds__(256) embedding8_kernel(const void *__restrict_
     if (vec) {                                               // D % 16 == 0, q rows and out 16-byte aligned
         const int64_t chunks = D / 16, total = n_idx * chunks;
         for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-            const int64_t t = i / chunks, c = i - t * chunks;
+            int64_t t, c;
+            if (total < 0x7fffffffll) { const uint32_t t32 = (uint32_t)i / (uint32_t)chunks; t = t32; c = (uint32_t)i - t32 * (uint32_t)chunks; }
+            else { t = i / chunks; c = i - t * chunks; }
             const int64_t row = load_index(idx, idx64, t);
             __align__(16) T vals[16];
             if (row < 0 || row >= V || row == padding_idx) {
