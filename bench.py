@@ -117,6 +117,13 @@ def cpu_layer_setup(cfg, M, seed=0):
     return layer
 
 
+def cpu_threads():
+    """All host cores for the CPU arms, whatever OMP_NUM_THREADS the launcher exported (torch.distributed.run sets 1);
+    returns the number of threads the C oracle's OpenMP loops will use."""
+    from oracle import oracle_c
+    return int(oracle_c.lib().o_threads(os.cpu_count() or 1))
+
+
 def cpu_layer_pass(layer):
     from oracle import oracle_c
     for name, n, k, packed, absmax, x, scratch in layer:
@@ -126,6 +133,7 @@ def cpu_layer_pass(layer):
 def cpu_baseline(cfg, M, budget_s=12.0):
     """GB/s of the reference CPU algorithm (C port, OpenMP on all cores) on one layer, scaled per byte."""
     from mps_bitsandbytes_b200 import stack as S
+    cores = cpu_threads()
     layer = cpu_layer_setup(cfg, M)
     cpu_layer_pass(layer)                                     # warm-up
     best, t_end, reps = float("inf"), time.perf_counter() + budget_s, 0
@@ -135,7 +143,7 @@ def cpu_baseline(cfg, M, budget_s=12.0):
         best = min(best, time.perf_counter() - t0)
         reps += 1
     nbytes = S.algorithmic_bytes(cfg, M, layers=1)           # same byte count per layer as the GPU arm
-    return {"value": nbytes / best / 1e9, "unit": "GB/s", "cores": os.cpu_count(), "kind": "port",
+    return {"value": nbytes / best / 1e9, "unit": "GB/s", "cores": cores, "kind": "port",
             "sample": f"1 of {cfg.layers} layers ({nbytes / 1e6:.0f} MB, 7 linears, random codes, absmax already expanded to "
                       f"fp32), best of {reps}, C oracle of functional.py:752-773 with OpenMP"}
 
@@ -155,6 +163,7 @@ def run_reference(args, cfg):
     if rank != 0:
         return
     from mps_bitsandbytes_b200 import stack as S
+    cores = cpu_threads()
     layer = cpu_layer_setup(cfg, args.batch)
     for _ in range(max(args.warmup, 1)):
         cpu_layer_pass(layer)
@@ -170,7 +179,7 @@ def run_reference(args, cfg):
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
         "config": workload_config(cfg, args.batch, args.layers or cfg.layers, args.gpus),
-        "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": os.cpu_count(), "kind": "port", "sample": sample},
+        "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0}))
 

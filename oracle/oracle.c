@@ -15,6 +15,7 @@
  * (-ffp-contract=off: no fused multiply-add may replace a rounded multiply and add.)
  */
 #include <math.h>
+#include <omp.h>
 #include <stdint.h>
 #include <stdlib.h>
 #include <string.h>
@@ -264,4 +265,11 @@ int64_t o_prove_nf4_buckets(int64_t stride) {
         bad += (got != o_nearest_by_threshold(v, 0, t));
     }
     return bad;
+}
+
+/* Thread count of the OpenMP loops above.  A launcher may export OMP_NUM_THREADS=1 (torch.distributed.run does); the
+ * timed CPU baseline sets the count explicitly and reports what it got.  n <= 0: query only. */
+int o_threads(int n) {
+    if (n > 0) omp_set_num_threads(n);
+    return omp_get_max_threads();
 }
