@@ -269,7 +269,11 @@ int mpsbnb_gemm_4bit(const void *x, int x_dtype, int64_t M, const uint8_t *packe
  *    operation): make it before any stream capture that will hold later calls.
  *  - Calls that may overlap in time on different streams of one device race on the array;
  *    same-stream calls are ordered.  Nothing in the array needs to start at zero.
+ *  - The resolved address is cached per device.  After cudaDeviceReset() the context it
+ *    belonged to is gone: call mpsbnb_gemm_4bit_static_forget() so that the next call
+ *    resolves it again.
  * Results are identical to mpsbnb_gemm_4bit (same kernels, same order). */
+void mpsbnb_gemm_4bit_static_forget(void);
 size_t mpsbnb_gemm_4bit_static_max_bytes(void);
 size_t mpsbnb_gemm_4bit_static_bytes(const void *x, int64_t M, int64_t N, int64_t K);
 int mpsbnb_gemm_4bit_static(const void *x, int x_dtype, int64_t M, const uint8_t *packed,
@@ -308,6 +312,11 @@ int mpsbnb_dequantize_rowwise(const int8_t *q, const float *scales, int64_t rows
 int mpsbnb_double_quant(const void *A, int a_dtype, int64_t rows, int64_t cols,
                         const float *row_stats_in, const float *col_stats_in, int8_t *out_row,
                         int8_t *out_col, float *row_stats_out, float *col_stats_out, void *stream);
+/* functional.py:866-889 dequant_absmax (tensor form): out[r, b] = float(q[r, b]) * scales[r, b / blocksize],
+ * q int8 [rows, nblk], scales fp32 [rows, ndq] with ndq >= ceil(nblk / blocksize), out fp32 [rows, nblk].
+ * (No division by 127: the reference multiplies by the stored scale as it is.) */
+int mpsbnb_dequant_absmax(const int8_t *q, const float *scales, int64_t rows, int64_t nblk, int64_t ndq,
+                          int blocksize, float *out, void *stream);
 /* functional.py:896-924 quantize_colrow: q = round(W * 127 / sqrt(r[n] c[k])). */
 int mpsbnb_quantize_colrow(const void *W, int w_dtype, int64_t rows, int64_t cols, int8_t *q,
                            float *row_absmax, float *col_absmax, void *stream);

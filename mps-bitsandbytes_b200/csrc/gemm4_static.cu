@@ -16,6 +16,10 @@
 //    streams) that can overlap in time race on the scratch and give wrong results; order them
 //    with events or use mpsbnb_gemm_4bit with separate workspaces.
 //  * Nothing in the scratch has to start at zero: every byte a call reads it has written first.
+//  * The looked-up address is cached per device for the life of the process.  cudaDeviceReset
+//    destroys the context the address belongs to; a process that resets a device must call
+//    mpsbnb_gemm_4bit_static_forget() afterwards, which drops the cache so that the next call
+//    looks the address up again.
 #include <atomic>
 
 #include "ops.cuh"
@@ -57,8 +61,13 @@ using namespace mpsbnb;
 
 extern "C" size_t mpsbnb_gemm_4bit_static_max_bytes(void) { return STATIC_SCRATCH_BYTES; }
 
+extern "C" void mpsbnb_gemm_4bit_static_forget(void) {
+    for (int d = 0; d < STATIC_MAX_DEVICES; ++d) g_scratch_ptr[d].store(nullptr, std::memory_order_release);
+}
+
 extern "C" size_t mpsbnb_gemm_4bit_static_bytes(const void *x, int64_t M, int64_t N, int64_t K) {
     if (M <= 0 || N <= 0 || K <= 0) return 0;
+    if (M > 0x7fffffff || N > 0x7fffffff || K > 0x7fffffff) return (size_t)-1;   // beyond any scratch
     return matrix_bytes(N, K) + (x_needs_copy(x, K) ? matrix_bytes(M, K) : 0);
 }
 
@@ -69,8 +78,8 @@ extern "C" int mpsbnb_gemm_4bit_static(const void *x, int x_dtype, int64_t M, co
     if (M < 0 || N < 0 || K <= 0) return K == 0 && M >= 0 && N >= 0 ? MPSBNB_ERR_UNSUPPORTED : MPSBNB_ERR_INVALID_ARG;
     if (M == 0 || N == 0) return MPSBNB_OK;
     if (x == nullptr || packed == nullptr || absmax == nullptr || y == nullptr) return MPSBNB_ERR_INVALID_ARG;
-    // sizes beyond the fixed array are refused before anything is enqueued
-    if (N > ((int64_t)1 << 40) / pitch8(K) || M > ((int64_t)1 << 40) / pitch8(K)) return MPSBNB_ERR_TOO_LARGE;
+    // sizes beyond the fixed array are refused before anything is enqueued (and before any size arithmetic)
+    if (M > 0x7fffffff || N > 0x7fffffff || K > 0x7fffffff) return MPSBNB_ERR_TOO_LARGE;
     if (mpsbnb_gemm_4bit_static_bytes(x, M, N, K) > STATIC_SCRATCH_BYTES) return MPSBNB_ERR_TOO_LARGE;
     unsigned char *scratch = nullptr;
     int rc = scratch_for_current_device(&scratch);

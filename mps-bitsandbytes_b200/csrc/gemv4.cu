@@ -114,7 +114,7 @@ template <typename T> __device__ __forceinline__ void store_out(void *y, int y_d
 // XT: x / MMA operand type.  MT: number of 8-wide batch tiles (M <= 8 MT).  R: 16-row tiles
 // per CTA pass (the x fragments of a block are reused for all R tiles).
 template <typename XT, int MT, int R>
-__global__ void __launch_bounds__(kWarps * 32, 2) gemv4_kernel(const Gemv4Params p) {
+__global__ void __launch_bounds__(kWarps * 32, 2) mpsbnb_decode4_direct_kernel(const Gemv4Params p) {
     extern __shared__ __align__(1024) unsigned char smem[];
     constexpr int ROWS = 16 * R;
     constexpr int RED_STRIDE = ROWS + 4;                    // conflict-free accumulator dump
@@ -273,13 +273,13 @@ static int launch_gemv4(const Gemv4Params &p, cudaStream_t st) {
     int dev = 0;
     MPSBNB_CUDA_TRY(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64 || !configured[dev]) {
-        MPSBNB_CUDA_TRY(cudaFuncSetAttribute(gemv4_kernel<XT, MT, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        MPSBNB_CUDA_TRY(cudaFuncSetAttribute(mpsbnb_decode4_direct_kernel<XT, MT, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
     const int ntiles = (p.N + ROWS - 1) / ROWS;
     int grid = sm_count() * 2;
     if (grid > ntiles) grid = ntiles;
-    gemv4_kernel<XT, MT, R><<<grid, kWarps * 32, smem, st>>>(p);
+    mpsbnb_decode4_direct_kernel<XT, MT, R><<<grid, kWarps * 32, smem, st>>>(p);
     return check_launch();
 }
 

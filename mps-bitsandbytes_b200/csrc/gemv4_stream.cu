@@ -335,7 +335,7 @@ struct SlotMap {
 };
 
 template <typename XT>
-__global__ void __launch_bounds__(SG_THREADS, 1) gemv4_stream_kernel(const __grid_constant__ StreamArgs a) {
+__global__ void __launch_bounds__(SG_THREADS, 1) mpsbnb_decode4_stream_kernel(const __grid_constant__ StreamArgs a) {
     extern __shared__ __align__(1024) unsigned char smem[];
     const uint32_t s_base = smem_u32(smem);
     const uint32_t s_red = s_base;                                   // 2 x SG_RED_BYTES
@@ -579,8 +579,8 @@ __global__ void __launch_bounds__(SG_THREADS, 1) gemv4_stream_kernel(const __gri
                     // int8 code * (second-level maximum / 127); 16 consecutive blocks see at most two maxima
                     const int8_t *aq = reinterpret_cast<const int8_t *>(L->absmax);
                     const int last = (b0 + 15 < L->nb ? b0 + 15 : L->nb - 1) - b0;
-                    const float f0 = __ldg(L->absmax2 + (i0 >> 8)) * (1.0f / 127.0f);
-                    const float f1 = __ldg(L->absmax2 + ((i0 + last) >> 8)) * (1.0f / 127.0f);
+                    const float f0 = __fdiv_rn(__ldg(L->absmax2 + (i0 >> 8)), 127.0f);       // divide first, as functional.py:592-593
+                    const float f1 = __fdiv_rn(__ldg(L->absmax2 + ((i0 + last) >> 8)), 127.0f);
                     const int split = (int)(((i0 >> 8) + 1) * 256 - i0);          // first j that uses f1
                     uint32_t raw[4];
                     if (b0 + 16 <= L->nb && (i0 & 3) == 0) {
@@ -968,7 +968,7 @@ static int launch_stream(StreamArgs &args, cudaStream_t st, bool pdl = false, bo
     int dev = 0;
     MPSBNB_CUDA_TRY(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64 || configured[dev] < smem) {
-        MPSBNB_CUDA_TRY(cudaFuncSetAttribute(gemv4_stream_kernel<XT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+        MPSBNB_CUDA_TRY(cudaFuncSetAttribute(mpsbnb_decode4_stream_kernel<XT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
         if (dev >= 0 && dev < 64) configured[dev] = 227 * 1024;
     }
     int grid = sm_count();
@@ -986,7 +986,7 @@ static int launch_stream(StreamArgs &args, cudaStream_t st, bool pdl = false, bo
         attr[0].val.programmaticStreamSerializationAllowed = 1;
     }
     cfg.attrs = attr; cfg.numAttrs = (pdl || cooperative) ? 1 : 0;
-    MPSBNB_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemv4_stream_kernel<XT>, args));
+    MPSBNB_CUDA_TRY(cudaLaunchKernelEx(&cfg, mpsbnb_decode4_stream_kernel<XT>, args));
     return check_launch();
 }
 

@@ -140,7 +140,7 @@ struct TgSlots {
 };
 
 template <typename XT, int NB>
-__global__ void __launch_bounds__(TG_THREADS, 1) gemv4_tc_kernel(const __grid_constant__ TcArgs a) {
+__global__ void __launch_bounds__(TG_THREADS, 1) mpsbnb_decode4_tmem_kernel(const __grid_constant__ TcArgs a) {
     // NB = batch rows the x tile and the accumulators hold (the UMMA N): 16 or 32
     constexpr int X_BYTES = NB * TG_STAGE_K * 2;                     // four [NB x 64] atoms of NB * 128 bytes
     constexpr int XS_BYTES = X_BYTES + TG_A_BYTES;
@@ -660,7 +660,7 @@ static int tc_launch_nb(TcArgs &args, int grid, cudaStream_t st, bool pdl) {
     int dev = 0;
     MPSBNB_CUDA_TRY(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64 || !configured[dev]) {
-        MPSBNB_CUDA_TRY(cudaFuncSetAttribute(gemv4_tc_kernel<XT, NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, TG_SMEM_BYTES));
+        MPSBNB_CUDA_TRY(cudaFuncSetAttribute(mpsbnb_decode4_tmem_kernel<XT, NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, TG_SMEM_BYTES));
         if (dev >= 0 && dev < 64) configured[dev] = 1;
     }
     cudaLaunchConfig_t cfg;
@@ -670,7 +670,7 @@ static int tc_launch_nb(TcArgs &args, int grid, cudaStream_t st, bool pdl) {
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr; cfg.numAttrs = pdl ? 1 : 0;
-    MPSBNB_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemv4_tc_kernel<XT, NB>, args));
+    MPSBNB_CUDA_TRY(cudaLaunchKernelEx(&cfg, mpsbnb_decode4_tmem_kernel<XT, NB>, args));
     return check_launch();
 }
 // batch <= 16 runs the 16-column instance (half the x tile, more weight slots), 17 .. 32 the 32-column one

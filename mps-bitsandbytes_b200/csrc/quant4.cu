@@ -17,7 +17,7 @@
 namespace mpsbnb {
 
 // Largest v for which code i (and not i+1) is the first minimiser of |v - code|:
-// derived by oracle/oracle.c:o_nf4_thresholds, checked by tests/test_thresholds.py.
+// derived by oracle/oracle.c:o_nf4_thresholds, checked by tests/test_cpu_library.py.
 #define NF4_T0 -0x1.b239b2p-1f
 #define NF4_T1 -0x1.38a4e2p-1f
 #define NF4_T2 -0x1.d709p-2f
@@ -173,7 +173,8 @@ quantize4_fast_kernel(const T *__restrict__ A, int64_t rows, int64_t cols, int64
                 if (live && (lane & (LPB - 1)) == 0) absmax_out[blk] = a;
             }
             uint32_t word = 0;
-            if (a >= 1e-30f && a <= 1e30f && absmax_in == nullptr) {   // range covered by the proof
+            if (a > 1e-8f && a <= 1e30f && absmax_in == nullptr) {   // a is a 16-bit input's magnitude: covered by the proof
+                                                                     // (a == 1e-8f is the clamp, not an input value: exact division)
                 const float r = __frcp_rn(a);
 #pragma unroll
                 for (int j = 0; j < 8; ++j) word |= code_fast<QT>(block_div<true>(x[j], a, r), nf4_tab) << (4 * j);

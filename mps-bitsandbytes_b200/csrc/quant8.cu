@@ -354,6 +354,24 @@ extern "C" int mpsbnb_dequantize_rowwise(const int8_t *q, const float *scales, i
     return check_launch();
 }
 
+__global__ void dequant_absmax_kernel(const int8_t *__restrict__ q, const float *__restrict__ scales, int64_t rows,
+                                      int64_t nblk, int64_t ndq, int blocksize, float *__restrict__ out) {
+    const int64_t total = rows * nblk;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = i / nblk, b = i - r * nblk;
+        out[i] = __fmul_rn((float)q[i], scales[r * ndq + b / blocksize]);
+    }
+}
+
+extern "C" int mpsbnb_dequant_absmax(const int8_t *q, const float *scales, int64_t rows, int64_t nblk, int64_t ndq,
+                                     int blocksize, float *out, void *stream) {
+    if (rows < 0 || nblk < 0 || blocksize <= 0) return MPSBNB_ERR_INVALID_ARG;
+    if (rows == 0 || nblk == 0) return MPSBNB_OK;
+    if (q == nullptr || scales == nullptr || out == nullptr || ndq < (nblk + blocksize - 1) / blocksize) return MPSBNB_ERR_INVALID_ARG;
+    dequant_absmax_kernel<<<grid_1d(rows * nblk), 256, 0, (cudaStream_t)stream>>>(q, scales, rows, nblk, ndq, blocksize, out);
+    return check_launch();
+}
+
 extern "C" int mpsbnb_double_quant(const void *A, int a_dtype, int64_t rows, int64_t cols,
                                    const float *row_stats_in, const float *col_stats_in, int8_t *out_row,
                                    int8_t *out_col, float *row_stats_out, float *col_stats_out, void *stream) {

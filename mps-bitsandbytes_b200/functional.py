@@ -50,6 +50,13 @@ def _check_device(tensor: Tensor, operation: str = "operation"):
             f"got '{tensor.device.type}'. Move tensor with .to('cuda')")
 
 
+def _need(name: str, t: Optional[Tensor], count: int, what: str):
+    """Raises the shape error the reference raises (there by broadcasting / indexing) when a caller-supplied
+    tensor holds fewer elements than the kernel is going to read: the kernels take raw pointers."""
+    if t is not None and t.numel() < count:
+        raise ValueError(f"{name} has {t.numel()} elements, {what} needs {count}")
+
+
 def _as_float(t: Tensor) -> Tensor:
     """Kernels take fp16 / bf16 / fp32; anything else is widened to fp32 as the reference's .float()."""
     return t if t.dtype in _FLOAT_DTYPES else t.float()
@@ -290,6 +297,7 @@ def quantize_blockwise(
     am_in = None
     if absmax is not None:
         am_in = absmax.to(device=A.device, dtype=torch.float32).contiguous().flatten()
+        _need("absmax", am_in, nblk, "quantize_blockwise")
         am = am_in
     else:
         am = torch.empty(nblk, dtype=torch.float32, device=A.device)
@@ -377,6 +385,7 @@ def dequantize_rowwise(quantized: Tensor, scales: Tensor, dtype: torch.dtype = t
     cols = q.shape[-1]
     rows = q.numel() // cols if cols else 0
     s = scales.to(device=q.device, dtype=torch.float32).contiguous().view(-1)
+    _need("scales", s, rows, "dequantize_rowwise")
     out = torch.empty(q.shape, dtype=dtype, device=q.device)
     with torch.cuda.device(q.device):
         N.check(N.lib().mpsbnb_dequantize_rowwise(N.ptr(q), N.ptr(s), N.i64(rows), N.i64(cols), N.ptr(out),
@@ -410,6 +419,7 @@ def dequantize_fp8_e4m3(quantized: Tensor, scales: Tensor, dtype: torch.dtype = 
     q = quantized.contiguous()
     rows, cols = q.shape
     s = scales.to(device=q.device, dtype=torch.float32).contiguous()
+    _need("scales", s, rows, "dequantize_fp8_e4m3")
     out = torch.empty(rows, cols, dtype=dtype, device=q.device)
     with torch.cuda.device(q.device):
         N.check(N.lib().mpsbnb_dequantize_fp8_e4m3(N.ptr(q), N.ptr(s), N.i64(rows), N.i64(cols), N.ptr(out),
@@ -460,7 +470,15 @@ def matmul_4bit(
     y = torch.empty(m, n, dtype=y_dtype, device=A.device)
     am, am2 = _expand_absmax(quant_state.absmax.to(A.device), quant_state.state2)
     packed = B.contiguous()
+    if packed.dtype != torch.uint8:
+        packed = packed.to(torch.uint8)       # quant_storage other than uint8 holds the byte VALUES (functional.py:299-300)
     bs, qt = quant_state.blocksize, N.qt(quant_state.quant_type)
+    kp = _padded(k, bs)
+    _need("packed weight", packed, n * (kp // 2), "matmul_4bit")
+    _need("absmax", am, n * (kp // bs), "matmul_4bit")
+    if am2 is not None:
+        _need("second-level absmax", am2, (n * (kp // bs) + 255) // 256, "matmul_4bit")
+    _need("bias", b, n, "matmul_4bit")
     lib = N.lib()
     with torch.cuda.device(A.device):
         if bs == 64 and m <= lib.mpsbnb_gemv_4bit_max_m():
@@ -506,6 +524,8 @@ def matmul_int8(A: Tensor, B: Tensor, A_scales: Tensor, B_scales: Tensor,
         raise RuntimeError(f"shape mismatch: A is {tuple(a.shape)}, B is {tuple(b.shape)}")
     sa = A_scales.to(device=a.device, dtype=torch.float32).contiguous().view(-1)
     sb = B_scales.to(device=a.device, dtype=torch.float32).contiguous().view(-1)
+    _need("A_scales", sa, m, "matmul_int8")
+    _need("B_scales", sb, n, "matmul_int8")
     y = torch.empty(m, n, dtype=dtype, device=a.device)
     lib = N.lib()
     with torch.cuda.device(a.device):
@@ -527,6 +547,11 @@ def _linear_int8(x: Tensor, w: Tensor, row_scales: Tensor, col_scales: Optional[
     r = row_scales.to(device=x.device, dtype=torch.float32).contiguous().view(-1)
     c = None if col_scales is None else col_scales.to(device=x.device, dtype=torch.float32).contiguous().view(-1)
     b = None if bias is None else bias.to(device=x.device, dtype=op).contiguous()
+    if x.shape[-1] != k:
+        raise RuntimeError(f"input has {x.shape[-1]} features, weight expects {k}")
+    _need("weight_row_scales", r, n, "the int8 linear")
+    _need("weight_col_scales", c, k, "the int8 linear")
+    _need("bias", b, n, "the int8 linear")
     y = torch.empty(m, n, dtype=dtype, device=x.device)
     lib = N.lib()
     with torch.cuda.device(x.device):
@@ -551,6 +576,10 @@ def matmul_fp8_e4m3(input: Tensor, weight: Tensor, weight_scales: Tensor,
     m = x2.shape[0]
     s = weight_scales.to(device=x.device, dtype=torch.float32).contiguous().view(-1)
     b = None if bias is None else bias.to(device=x.device, dtype=op).contiguous()
+    if x.shape[-1] != k:
+        raise RuntimeError(f"input has {x.shape[-1]} features, weight expects {k}")
+    _need("weight_scales", s, n, "matmul_fp8_e4m3")
+    _need("bias", b, n, "matmul_fp8_e4m3")
     y = torch.empty(m, n, dtype=dtype, device=x.device)
     lib = N.lib()
     with torch.cuda.device(x.device):
@@ -585,6 +614,8 @@ def double_quant(
     dev = A.device
     rs_in = None if row_stats is None else row_stats.to(device=dev, dtype=torch.float32).contiguous()
     cs_in = None if col_stats is None else col_stats.to(device=dev, dtype=torch.float32).contiguous()
+    _need("row_stats", rs_in, rows, "double_quant")
+    _need("col_stats", cs_in, cols, "double_quant")
     rs = rs_in if rs_in is not None else torch.empty(rows, dtype=torch.float32, device=dev)
     cs = cs_in if cs_in is not None else torch.empty(cols, dtype=torch.float32, device=dev)
     new_row = torch.empty(rows, cols, dtype=torch.int8, device=dev) if out_row is None else None
@@ -605,11 +636,18 @@ def dequant_absmax(absmax_quant: Tensor, absmax_scales, blocksize: int = 256) ->
         return dequantize_blockwise(absmax_quant, absmax_scales)
     _check_device(absmax_quant, "dequant_absmax")
     one_d = absmax_quant.dim() == 1
-    q = absmax_quant.unsqueeze(0) if one_d else absmax_quant
-    s = absmax_scales.unsqueeze(0) if one_d else absmax_scales
-    nblk = q.shape[1]
-    idx = torch.arange(nblk, device=q.device) // blocksize
-    out = q.float() * s.float()[:, idx]
+    q = (absmax_quant.unsqueeze(0) if one_d else absmax_quant).contiguous()
+    if q.dtype != torch.int8:
+        q = q.to(torch.int8)
+    rows, nblk = q.shape[0], q.numel() // max(q.shape[0], 1)
+    s = absmax_scales.to(device=q.device, dtype=torch.float32).contiguous().view(rows, -1)
+    ndq = s.shape[1]
+    if ndq * blocksize < nblk:
+        raise ValueError(f"absmax_scales has {ndq} groups per row, {nblk} blocks need {(nblk + blocksize - 1) // blocksize}")
+    out = torch.empty(rows, nblk, dtype=torch.float32, device=q.device)
+    with torch.cuda.device(q.device):
+        N.check(N.lib().mpsbnb_dequant_absmax(N.ptr(q), N.ptr(s), N.i64(rows), N.i64(nblk), N.i64(ndq), C.c_int(blocksize),
+                                              N.ptr(out), N.stream()), "dequant_absmax")
     return out.squeeze(0) if one_d else out
 
 
@@ -637,6 +675,8 @@ def dequantize_colrow(quantized: Tensor, row_scales: Tensor, col_scales: Tensor,
     rows, cols = q.shape
     r = row_scales.to(device=q.device, dtype=torch.float32).contiguous()
     c = col_scales.to(device=q.device, dtype=torch.float32).contiguous()
+    _need("row_scales", r, rows, "dequantize_colrow")
+    _need("col_scales", c, cols, "dequantize_colrow")
     out = torch.empty(rows, cols, dtype=dtype, device=q.device)
     with torch.cuda.device(q.device):
         N.check(N.lib().mpsbnb_dequantize_colrow(N.ptr(q), N.ptr(r), N.ptr(c), N.i64(rows), N.i64(cols),

@@ -472,6 +472,15 @@ class LayerStack:
             return self.h_out
         return self.hbuf[self.layers % self._nbuf] if self._stream else self.h
 
+    def check_status(self, reset: bool = True) -> int:
+        """Device status word of this stack's GPU: 0, or the code a kernel recorded when one of its bounded waits ran
+        out (a peer that never raised its flag, a stage that never arrived).  A step whose status is not 0 returned
+        with a wrong result; callers that need to know must poll this (it synchronises the device)."""
+        with torch.cuda.device(self.device):
+            st = C.c_int(0)
+            N.check(N.lib().mpsbnb_device_status(C.byref(st), C.c_int(1 if reset else 0)), "device_status")
+        return int(st.value)
+
     def output(self) -> torch.Tensor:
         """h after the last layer of the latest step."""
         return self._result()

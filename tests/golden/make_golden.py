@@ -407,7 +407,9 @@ def modules(ref_path):
 
 if __name__ == "__main__":
     args = [a for a in sys.argv[1:] if not a.startswith("--")]
-    path = args[0] if args else "/root/reference"
+    if not args:
+        sys.exit("usage: make_golden.py <path to a checkout of mps-bitsandbytes v0.7.0> [--only-modules]")
+    path = args[0]
     if "--only-modules" in sys.argv:
         modules(path)
     else:

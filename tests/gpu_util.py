@@ -16,9 +16,18 @@ def to_np(t: torch.Tensor) -> np.ndarray:
 
 
 def rel_err(y, ref) -> float:
-    """max |y - ref| / max |ref|: the matmul parity norm (bound 1e-2)."""
+    """The matmul parity figure (bound 1e-2): the larger of two norms,
+      max |y - ref| / max |ref|                     (error against the largest output), and
+      max_i |y_i - ref_i| / (|ref_i| + rms(ref))    (<= 1e-2 is allclose(rtol=1e-2, atol=1e-2 rms(ref)):
+                                                     a small output may not be wholly wrong)."""
     y = np.asarray(y, np.float32); ref = np.asarray(ref, np.float32)
-    return float(np.abs(y - ref).max() / max(float(np.abs(ref).max()), 1e-30))
+    if ref.size == 0:
+        return 0.0
+    d = np.abs(y - ref)
+    n1 = float(d.max() / max(float(np.abs(ref).max()), 1e-30))
+    rms = float(np.sqrt(np.mean(np.square(ref.astype(np.float64)))))
+    n2 = float((d / (np.abs(ref) + max(rms, 1e-30))).max())
+    return max(n1, n2)
 
 
 def assert_device_ok():

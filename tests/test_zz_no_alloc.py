@@ -67,6 +67,15 @@ def test_static_matches_workspace_entry_point_twice(M, N_, K, qt, dq):
     assert torch.equal(got1, want)
     assert torch.equal(gotm, want2)
     assert torch.equal(got2, want)
+    # ... and against the CPU oracle of the reference's path (dequantise the whole weight, then matmul)
+    if x.dtype == torch.float16:
+        import numpy as np
+        from oracle import oracle_c
+        am = absmax.cpu().numpy() if absmax2 is None else oracle_c.dequantize_absmax(absmax.cpu().numpy(), absmax2.cpu().numpy())
+        ref = oracle_c.matmul_4bit_f16(x.cpu().numpy(), packed.cpu().numpy(), am.astype(np.float32), N_, K, 64, qt,
+                                       bias=bias.cpu().numpy())
+        err = np.abs(got2.cpu().numpy().astype(np.float32) - ref.astype(np.float32)).max() / np.abs(ref.astype(np.float32)).max()
+        assert err <= 1e-2, err
     code = C.c_int(0)
     assert lib.mpsbnb_device_status(C.byref(code), C.c_int(0)) == 0 and code.value == 0
 
@@ -87,3 +96,10 @@ def test_static_refuses_what_does_not_fit():
     assert bool((y == 7.0).all())
     rc, _ = _static(N, lib, x, packed, absmax, absmax2, bias, 16, 1 << 30, 1 << 30, "nf4", y=y)
     assert rc == -5
+    # sizes beyond 32-bit are refused before any size arithmetic
+    rc, _ = _static(N, lib, x, packed, absmax, absmax2, bias, 16, 64, (1 << 63) - 1, "nf4", y=y)
+    assert rc == -5
+    lib.mpsbnb_gemm_4bit_static_forget()                        # drops the cached address; the next call resolves it again
+    rc, y2 = _static(N, lib, x, packed, absmax, absmax2, bias, 16, 64, 128, "nf4")
+    torch.cuda.synchronize()
+    assert rc == 0 and bool(torch.isfinite(y2.float()).all())
