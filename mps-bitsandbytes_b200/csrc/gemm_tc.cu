@@ -312,6 +312,9 @@ extern "C" int mpsbnb_device_status(int *status_out, int reset) {
     const int rc3 = xchg_status_fetch(&other, reset != 0);
     if (rc3 != MPSBNB_OK) return rc3;
     if (*status_out == 0) *status_out = other;
+    const int rc4 = wq_status_fetch(&other, reset != 0);
+    if (rc4 != MPSBNB_OK) return rc4;
+    if (*status_out == 0) *status_out = other;
     return MPSBNB_OK;
 }
 

@@ -61,6 +61,16 @@ constexpr int SG_MAX_M = 8;
 // stream_status_fetch() on behalf of mpsbnb_device_status()
 static __device__ int g_stream_status = 0;
 
+#ifdef MPSBNB_TRACE
+// Development aid (compiled in with -DMPSBNB_TRACE only): per segment, when CTA 0's first loader began and ended its
+// wait for the segment's input flags, and when this GPU raised its own flag; nanoseconds of %globaltimer.
+static __device__ unsigned long long g_trace[3 * 256];
+__device__ __forceinline__ unsigned long long trace_now() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
+#define MPSBNB_TRACE_SET(slot, seg) do { if ((seg) >= 0 && (seg) < 256) g_trace[(slot) * 256 + (seg)] = trace_now(); } while (0)
+#else
+#define MPSBNB_TRACE_SET(slot, seg) do { } while (0)
+#endif
+
 
 struct StreamLinear {
     CUtensorMap map;          // packed weights as [N][row_bytes] bytes; box 128 B x 32 rows, 128-byte swizzle
@@ -544,6 +554,7 @@ __global__ void __launch_bounds__(SG_THREADS, 1) mpsbnb_decode4_stream_kernel(co
                     // every tile of this rank's shard has been stored (each store was fenced before its count)
                     if (a.ep.nranks > 1) __threadfence_system(); else __threadfence();
                     if (lane == 0) *a.ep.counter = 0;
+                    if (lane == 0) MPSBNB_TRACE_SET(2, seg + 1);
                     if (a.ep.peer_flags != nullptr && lane < a.ep.nranks)
                         asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(a.ep.peer_flags[lane] + a.ep.rank), "r"((*a.ep.step) * a.ep.mul + a.ep.add + seg) : "memory");
                 }
@@ -643,6 +654,7 @@ __global__ void __launch_bounds__(SG_THREADS, 1) mpsbnb_decode4_stream_kernel(co
                     // in the N-sharded stack, on the others.  Wait (bounded) for their flags.
                     const int expect = (*a.wait_step) * a.wait_mul + a.wait_add + my_L->segment;
                     bool arrived = true;
+                    if (blockIdx.x == 0 && me == 0 && lane == 0) MPSBNB_TRACE_SET(0, my_L->segment);
                     if (lane < a.wait_n) {
                         const long long t0 = clock64();
                         for (;;) {
@@ -656,6 +668,7 @@ __global__ void __launch_bounds__(SG_THREADS, 1) mpsbnb_decode4_stream_kernel(co
                     arrived = __all_sync(0xffffffffu, arrived);
                     asm volatile("fence.proxy.async;" ::: "memory");      // x is then read by bulk copies (async proxy)
                     if (!arrived) { atomicExch(&g_stream_status, 207); *abort_flag = 1; break; }
+                    if (blockIdx.x == 0 && me == 0 && lane == 0) MPSBNB_TRACE_SET(1, my_L->segment);
                     ready_seg = my_L->segment;
                 }
 #pragma unroll
@@ -998,6 +1011,12 @@ int stream_status_fetch(int *out, bool reset) {
     }
     return MPSBNB_OK;
 }
+
+#ifdef MPSBNB_TRACE
+extern "C" int mpsbnb_debug_trace(unsigned long long *out768) {
+    return cudaMemcpyFromSymbol(out768, g_trace, sizeof(unsigned long long) * 768) == cudaSuccess ? 0 : -3;
+}
+#endif
 
 // 0: TMA ring + mma.sync / dot products (default); 1: TMA ring + tcgen05 with the expanded weights in tensor memory
 static int g_decode_kernel = -1;

@@ -17,6 +17,15 @@ int gemm_16bit(const void *a, int64_t lda, const void *b, int64_t ldb, int ab_dt
                const float *row_scale, const float *col_scale, const void *bias, int bias_dtype, void *y, int64_t ldy,
                int y_dtype, cudaStream_t st);
 
+// fused dequantise-GEMM (gemm_wq.cu): mode 0 = 4-bit packed, 1 = int8 rows, 2 = FP8 E4M3 rows
+bool gemm_wq_supported(const void *x, int64_t ldx, const void *wq, int64_t row_bytes);
+int gemm_wq(int mode, const void *x, int64_t ldx, int x_dtype, int64_t M, const void *wq, int64_t row_bytes,
+            const void *absmax, const float *absmax2, const float *wscale, float wscale_mul, int wscale_sqrt, int64_t N,
+            int64_t K, int quant_type, const void *bias, void *y, int y_dtype, cudaStream_t st);
+int scale_cols_16bit(const void *x, int64_t M, int64_t K, int64_t ldx, const float *c, void *out, int64_t ldo, int dtype,
+                     cudaStream_t st);
+int wq_status_fetch(int *out, bool reset);
+
 int gemv4_stream_single(const void *x, int x_dtype, int64_t M, const uint8_t *packed, const void *absmax,
                         const float *absmax2, int64_t N, int64_t K, int quant_type, const void *bias, void *y,
                         int y_dtype, cudaStream_t st);

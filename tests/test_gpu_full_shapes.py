@@ -116,7 +116,8 @@ def test_config4_outlier_split_full_size():
     lin = torch.nn.Linear(K, Nn, bias=False, device="cuda", dtype=torch.float16)
     lin.weight.data = w
     layer = bnb.OutlierAwareLinear.from_linear(lin)
-    assert int(layer.outlier_indices.numel()) == int(cols.numel())
+    found = set(layer.outlier_indices.tolist())                 # the 20 scaled columns, plus columns whose largest weight
+    assert set(cols.tolist()) <= found and len(found) < 200     # among 16384 rows happens to pass the 6 x mean rule
     y = layer(x)
     rows = np.sort(np.random.default_rng(5).choice(M, 32, replace=False))
     ref = O.outlier_linear(to_np(x)[rows], to_np(layer.weight_int8), to_np(layer.weight_scales),
