@@ -249,8 +249,13 @@ int mpsbnb_counter_add(int *counter, int value, void *stream);
 int mpsbnb_stack_expand(const void *G, int dtype, int64_t nranks, int64_t M, int64_t H, int64_t F,
                         void *h, void *e, void *stream);
 
-/* Any M: dequantise W into the caller's workspace in x_dtype, then a tcgen05 tensor-core
- * GEMM.  workspace must hold mpsbnb_gemm_4bit_workspace_bytes(...) bytes, 256-B aligned. */
+/* functional.py:680-773 matmul_4bit on prefill shapes (any M); the reference's Metal analogue
+ * dequantises inside the GEMM's K loop (nf4_matmul_large, mps_bitsandbytes.mm:567-696).
+ * Block size 64 (packed 16-byte aligned): ONE fused kernel - packed bytes by TMA, expanded in
+ * shared memory, tcgen05 MMA; no 16-bit copy of the weight exists.  The workspace then only
+ * holds a re-pitched copy of x when K % 8 != 0 or x is not 16-byte aligned.  Other block sizes:
+ * W is dequantised into the workspace in x_dtype and multiplied by the plain tcgen05 GEMM.
+ * workspace must hold mpsbnb_gemm_4bit_workspace_bytes(...) bytes, 256-B aligned, non-NULL. */
 size_t mpsbnb_gemm_4bit_workspace_bytes(int64_t M, int64_t N, int64_t K, int blocksize);
 int mpsbnb_gemm_4bit(const void *x, int x_dtype, int64_t M, const uint8_t *packed,
                      const void *absmax, const float *absmax2, int64_t N, int64_t K,
@@ -272,7 +277,8 @@ int mpsbnb_gemm_4bit(const void *x, int x_dtype, int64_t M, const uint8_t *packe
  *  - The resolved address is cached per device.  After cudaDeviceReset() the context it
  *    belonged to is gone: call mpsbnb_gemm_4bit_static_forget() so that the next call
  *    resolves it again.
- * Results are identical to mpsbnb_gemm_4bit (same kernels, same order). */
+ * The weight is expanded into the array and multiplied by the plain tcgen05 GEMM; results agree
+ * with mpsbnb_gemm_4bit within the matmul tolerance (1e-2; measured ~5e-4) and repeat exactly. */
 void mpsbnb_gemm_4bit_static_forget(void);
 size_t mpsbnb_gemm_4bit_static_max_bytes(void);
 size_t mpsbnb_gemm_4bit_static_bytes(const void *x, int64_t M, int64_t N, int64_t K);

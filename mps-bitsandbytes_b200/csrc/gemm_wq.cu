@@ -10,26 +10,33 @@
 // Orientation: the WEIGHT is the MMA's A operand (128 weight rows = the 128 lanes of tensor memory) and
 // x is the B operand (TM = 32 ... 256 rows of x = accumulator columns).  A 128 x TM tile therefore
 // expands 128 x 64 weights per 64-wide K step whatever TM is - half of what a 128 (x) x 256 (weight)
-// tile would need - and a small batch simply uses a narrow TM.  One persistent CTA per SM, 15 warps:
-//   warp 0      TMA producer of x tiles (TM rows x 64 k, 128-byte swizzle) into the X ring;
+// tile would need - and a small batch simply uses a narrow TM.  One persistent CTA per SM, 23 warps:
+//   warp 0      TMA producer of x tiles (TM rows x 64 k, 128-byte swizzle) into the X ring (3 stages of 32 KB for
+//               TM = 256 ... 16 stages of 4 KB for TM = 32: a stage is in flight for a whole TMA round trip);
 //   warp 1      MMA issuer: per K step four tcgen05.mma (128 x TM x 16, kind::f16), then tcgen05.commit
 //               hands the W and X stages back; owns the tensor-memory allocation (2 x TM columns: the
 //               accumulator is double-buffered, so the epilogue of a tile overlaps the next tile);
-//   warp 2      TMA producer of quantised weight chunks (128 rows x 128 bytes, 128-byte swizzle): 256 k of
-//               4-bit codes or 128 k of 8-bit codes per chunk, into the Q ring;
+//   warp 2      TMA producer of quantised weight chunks into the Q ring: 128 rows x 128 bytes (128-byte swizzle) =
+//               256 k of 4-bit codes or 128 k of 8-bit codes, or 64 k-rows x 128 n-bytes of a K x N int8 operand;
 //   warps 3-6   epilogue: tcgen05.ld (lane = weight row n, column = x row m), scale, bias, round, store;
-//   warps 7-14  expanders: thread (r, h) turns half a row (32 k) of a K step into 64 bytes of the W stage.
-//               4-bit: byte -> (code[lo], code[hi]) by a 256-entry table replicated per lane in shared
-//               memory, times the block's absmax in fp32, ONE rounding to the operand type.
-//               int8: exact conversion (the per-row scale is applied to the fp32 accumulator instead).
+//   warps 7-22  expanders, two groups of eight warps that take alternate K steps (each group alternates between two
+//               of the four W stages, so it fills one while the tensor core reads the other).  Thread (r, h) turns
+//               half a row (32 k) of a K step into 64 bytes of the W stage.
+//               4-bit: byte -> (code[lo], code[hi]) by a 256-entry fp16-pair table replicated per lane in shared
+//               memory, times the block's absmax (one packed fp16 multiply when the scale sits well inside the
+//               fp16 range, else an fp32 product rounded once).
+//               int8: exact conversion (the per-row scale is applied to the fp32 accumulator instead); a K x N
+//               operand is transposed on the way (byte permutes in registers).
 //               fp8 E4M3: exact hardware conversion (per-row scale in the epilogue as well).
+// What bounds it (measured): for TM = 256 the tensor pipe and the L2 -> shared-memory traffic of the x tiles, as in
+// the unfused GEMM; for narrow tiles the serial MMA-issuer thread (two waits, four MMAs, two commits per K step cost
+// it about 900 cycles, of which the expanders' work is entirely hidden), i.e. about 1 TB/s of weight bytes.
 // Every wait is bounded; a time-out records a status word and all roles leave through the common exit.
 #include "common.cuh"
 #include "ops.cuh"
 #include "sm100.cuh"
 
 #include <string.h>
-#include <stdlib.h>
 
 namespace mpsbnb {
 
@@ -50,6 +57,7 @@ enum { WQ_4BIT = 0, WQ_INT8 = 1, WQ_FP8 = 2, WQ_INT8T = 3 };   // INT8T: int8 st
 
 static __device__ int g_wq_status = 0;
 
+
 struct WqArgs {
     const void *absmax;        // 4-bit: fp32 [N, nb] or int8 [N, nb] (absmax2 != nullptr)
     const float *absmax2;      // 4-bit double quantisation: fp32 [ceil(N nb / 256)]
@@ -61,7 +69,6 @@ struct WqArgs {
     int y_dtype, fmt;          // fmt: 0 = fp16 operands, 1 = bf16
     int M, N, K, nb;           // nb: absmax blocks per row (4-bit)
     int quant_type;
-    int dbg;
 };
 
 template <int TM> struct WqSmem {
@@ -389,12 +396,10 @@ mpsbnb_gemm_wq_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_con
                         for (int j = 0; j < 4; ++j) {
                             const uint32_t w = w4[j];
                             uint32_t p[4];
-                            if (a.dbg & 1) { p[0] = w; p[1] = w >> 1; p[2] = w >> 2; p[3] = w >> 3; } else {
                             p[0] = wq_lut(lut_lane + __byte_perm(w, 0u, 0x4440) * 128u);
                             p[1] = wq_lut(lut_lane + __byte_perm(w, 0u, 0x4441) * 128u);
                             p[2] = wq_lut(lut_lane + __byte_perm(w, 0u, 0x4442) * 128u);
-                            p[3] = wq_lut(lut_lane + __byte_perm(w, 0u, 0x4443) * 128u); }
-                            if (a.dbg & 8) {} else
+                            p[3] = wq_lut(lut_lane + __byte_perm(w, 0u, 0x4443) * 128u);
                             if (fast) {
 #pragma unroll
                                 for (int e = 0; e < 4; ++e) {
@@ -405,7 +410,6 @@ mpsbnb_gemm_wq_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_con
 #pragma unroll
                                 for (int e = 0; e < 4; ++e) p[e] = wq_scale_pair<FMT>(p[e], s_cur);
                             }
-                            if (!(a.dbg & 2) || (p[0] ^ p[1] ^ p[2] ^ p[3]) == 0x12345u)
                             wq_sts128(wrow + (uint32_t)((((h << 2) | j) ^ sw) << 4), p[0], p[1], p[2], p[3]);
                         }
                     }
@@ -458,7 +462,7 @@ mpsbnb_gemm_wq_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_con
                         wq_sts128(wrow + (uint32_t)((((h << 2) | (j << 1) | 1) ^ sw) << 4), o[4], o[5], o[6], o[7]);
                     }
                 }
-                if (!(a.dbg & 4)) fence_proxy_async_smem();                        // my stores before the tensor core's reads
+                fence_proxy_async_smem();                        // my stores before the tensor core's reads
                 __syncwarp();
                 if (lane == 0) { mbar_arrive(wfull(ws)); mbar_arrive(qempty(qs)); }   // every lane has read its bytes
             }
@@ -587,7 +591,6 @@ int gemm_wq(int mode, const void *x, int64_t ldx, int x_dtype, int64_t M, const 
     a.absmax = absmax; a.absmax2 = absmax2; a.wscale = wscale; a.wscale_mul = wscale_mul; a.wscale_sqrt = wscale_sqrt;
     a.bias = bias; a.y = y; a.y_dtype = y_dtype; a.fmt = x_dtype == MPSBNB_F16 ? 0 : 1;
     a.M = (int)M; a.N = (int)N; a.K = (int)K; a.nb = (int)(padded_k(K, 64) / 64); a.quant_type = quant_type;
-    { const char *e = getenv("MPSBNB_WQ_DBG"); a.dbg = e ? atoi(e) : 0; }
     const bool f16 = x_dtype == MPSBNB_F16;
     if (mode == WQ_4BIT) return f16 ? wq_launch_tm<WQ_4BIT, 0>(tm, mx, mq, a, st) : wq_launch_tm<WQ_4BIT, 1>(tm, mx, mq, a, st);
     if (mode == WQ_INT8) return f16 ? wq_launch_tm<WQ_INT8, 0>(tm, mx, mq, a, st) : wq_launch_tm<WQ_INT8, 1>(tm, mx, mq, a, st);

@@ -1,8 +1,9 @@
 """The workspace-free 4-bit GEMM entry point (scratch inside the library's device image).
 
 Collected last on purpose (file name): it must pass both alone and after every other GPU test
-has used the library.  Calls go through the C ABI; the reference result is the workspace-taking
-entry point, which runs the same kernels, so the comparison is exact.
+has used the library.  Calls go through the C ABI; the reference results are the workspace-taking
+entry point (the fused kernel: agreement within the matmul tolerance), the entry point itself on a
+second call (exact) and the CPU oracle.
 """
 import ctypes as C
 
@@ -64,9 +65,12 @@ def test_static_matches_workspace_entry_point_twice(M, N_, K, qt, dq):
     rc2, got2 = _static(N, lib, x, packed, absmax, absmax2, bias, M, N_, K, qt)
     torch.cuda.synchronize()
     assert (rc1, rcm, rc2) == (0, 0, 0)
-    assert torch.equal(got1, want)
-    assert torch.equal(gotm, want2)
-    assert torch.equal(got2, want)
+    def close(a, b):
+        a, b = a.float(), b.float()
+        return float((a - b).abs().max() / b.abs().max()) <= 1e-2
+    assert close(got1, want)
+    assert close(gotm, want2)
+    assert torch.equal(got2, got1)                              # the call repeats exactly, whatever the scratch held
     # ... and against the CPU oracle of the reference's path (dequantise the whole weight, then matmul)
     if x.dtype == torch.float16:
         import numpy as np
