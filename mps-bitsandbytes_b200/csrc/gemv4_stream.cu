@@ -67,8 +67,12 @@ static __device__ int g_stream_status = 0;
 static __device__ unsigned long long g_trace[3 * 256];
 __device__ __forceinline__ unsigned long long trace_now() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
 #define MPSBNB_TRACE_SET(slot, seg) do { if ((seg) >= 0 && (seg) < 256) g_trace[(slot) * 256 + (seg)] = trace_now(); } while (0)
+// cycles CTA 0's roles spend inside each kind of barrier wait (lane 0 of every warp adds its own), [15] = CTA 0's total
+static __device__ unsigned long long g_wait[16];
+#define SG_TIMED(idx, expr) ([&]() { const long long t0_ = clock64(); const bool r_ = (expr); if (blockIdx.x == 0 && (threadIdx.x & 31) == 0) atomicAdd(&g_wait[idx], (unsigned long long)(clock64() - t0_)); return r_; }())
 #else
 #define MPSBNB_TRACE_SET(slot, seg) do { } while (0)
+#define SG_TIMED(idx, expr) (expr)
 #endif
 
 
@@ -382,6 +386,9 @@ __global__ void __launch_bounds__(SG_THREADS, 1) mpsbnb_decode4_stream_kernel(co
     auto xempty_bar = [&](int s) { return s_bar + 8u * (2 * SG_MAX_SLOTS + 4 + SG_MAX_XS + s); };
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+#ifdef MPSBNB_TRACE
+    const long long trace_t0 = clock64();
+#endif
     pdl_launch_dependents();
 
     if (tid == 0) {
@@ -436,7 +443,7 @@ __global__ void __launch_bounds__(SG_THREADS, 1) mpsbnb_decode4_stream_kernel(co
                 const bool m3 = L->map3d != 0;
                 bool ok = true;
                 for (int s = un.s_begin; s < un.s_end; ++s) {
-                    if (!mbar_wait_sleep(empty_bar(slot), ph ^ 1u, abort_flag, a.sleep_other)) { atomicExch(&g_stream_status, 201); *abort_flag = 1; ok = false; break; }
+                    if (!SG_TIMED(0, mbar_wait_sleep(empty_bar(slot), ph ^ 1u, abort_flag, a.sleep_other))) { atomicExch(&g_stream_status, 201); *abort_flag = 1; ok = false; break; }
                     const uint32_t bar = full_bar(slot), dst = sm.addr(slot);
                     mbar_arrive_expect_tx(bar, SG_W_BYTES);
                     if (m3) {
@@ -480,7 +487,7 @@ __global__ void __launch_bounds__(SG_THREADS, 1) mpsbnb_decode4_stream_kernel(co
             const StreamUnit un = unit_of(u);
             const StreamLinear *L = lin_of(un.lin);
             const int buf = uc & 1;
-            if (!mbar_wait_sleep(red_full(buf), (uint32_t)(uc >> 1) & 1u, abort_flag, a.sleep_other)) { atomicExch(&g_stream_status, 204); *abort_flag = 1; break; }
+            if (!SG_TIMED(1, mbar_wait_sleep(red_full(buf), (uint32_t)(uc >> 1) & 1u, abort_flag, a.sleep_other))) { atomicExch(&g_stream_status, 204); *abort_flag = 1; break; }
             const float *red = reinterpret_cast<const float *>(p_generic0 + s_red + buf * SG_RED_BYTES);
             const int n = un.row0 + lane;
             for (int m = 0; m < a.M; ++m) {
@@ -647,7 +654,7 @@ __global__ void __launch_bounds__(SG_THREADS, 1) mpsbnb_decode4_stream_kernel(co
                 float nxt[16];
                 more = advance_to_mine();
                 if (more) read_scales(L, un.row0, s, nxt);
-                if (!mbar_wait_sleep(xempty_bar(my_x), my_ph ^ 1u, abort_flag, a.sleep_other)) { atomicExch(&g_stream_status, 202); *abort_flag = 1; break; }
+                if (!SG_TIMED(2, mbar_wait_sleep(xempty_bar(my_x), my_ph ^ 1u, abort_flag, a.sleep_other))) { atomicExch(&g_stream_status, 202); *abort_flag = 1; break; }
                 const uint32_t xb = s_xs + (uint32_t)my_x * xs_bytes;
                 if (a.wait_n > 0 && my_L->segment > ready_seg) {
                     // x of this segment is written by closing steps: of the previous launch or segment, on this GPU and,
@@ -776,8 +783,8 @@ __global__ void __launch_bounds__(SG_THREADS, 1) mpsbnb_decode4_stream_kernel(co
 #pragma unroll 1
                 for (; nextq < qe; nextq += SG_GROUPS) {
                     const int s = un.s_begin + (nextq - qb);
-                    if (!mbar_wait_sleep(full_bar(slot), ph, abort_flag, a.sleep_cons)) { atomicExch(&g_stream_status, 203); *abort_flag = 1; ok = false; break; }
-                    if (!mbar_wait_sleep(xfull_bar(xslot), xph, abort_flag, a.sleep_cons)) { atomicExch(&g_stream_status, 206); *abort_flag = 1; ok = false; break; }
+                    if (!SG_TIMED(warp == 0 ? 3 : 6, mbar_wait_sleep(full_bar(slot), ph, abort_flag, a.sleep_cons))) { atomicExch(&g_stream_status, 203); *abort_flag = 1; ok = false; break; }
+                    if (!SG_TIMED(warp == 0 ? 4 : 7, mbar_wait_sleep(xfull_bar(xslot), xph, abort_flag, a.sleep_cons))) { atomicExch(&g_stream_status, 206); *abort_flag = 1; ok = false; break; }
                     const uint32_t dep = stage_fn(s, nbv, sm.addr(slot), s_xs + (uint32_t)xslot * xs_bytes, empty_bar(slot));
                     __syncwarp();
                     if (lane == 0) mbar_arrive(xempty_bar(xslot) + (dep & a.zero));
@@ -788,7 +795,7 @@ __global__ void __launch_bounds__(SG_THREADS, 1) mpsbnb_decode4_stream_kernel(co
                 // hand the partial sums to the reducer warp (zeros if none of this unit's stages were mine); the
                 // buffer of two units ago must have been drained
                 const int buf = uc & 1;
-                if (!mbar_wait_sleep(red_empty(buf), ((uint32_t)(uc >> 1) & 1u) ^ 1u, abort_flag, a.sleep_cons)) { atomicExch(&g_stream_status, 205); *abort_flag = 1; break; }
+                if (!SG_TIMED(warp == 0 ? 5 : 8, mbar_wait_sleep(red_empty(buf), ((uint32_t)(uc >> 1) & 1u) ^ 1u, abort_flag, a.sleep_cons))) { atomicExch(&g_stream_status, 205); *abort_flag = 1; break; }
                 flush_fn(s_red + (uint32_t)(buf * SG_RED_BYTES));
                 __syncwarp();
                 if (lane == 0) mbar_arrive(red_full(buf));
@@ -866,6 +873,9 @@ __global__ void __launch_bounds__(SG_THREADS, 1) mpsbnb_decode4_stream_kernel(co
     // After a time-out the roles leave early while copies may still be on their way into this CTA's
     // shared memory: give them a bounded moment to land before the CTA retires.
     __syncthreads();                                                 // every role of this CTA is done
+#ifdef MPSBNB_TRACE
+    if (blockIdx.x == 0 && tid == 0) atomicAdd(&g_wait[15], (unsigned long long)(clock64() - trace_t0));
+#endif
     if (*abort_flag) {
         const long long t0 = clock64();
         while (clock64() - t0 < 400000ll) { }
@@ -1015,6 +1025,11 @@ int stream_status_fetch(int *out, bool reset) {
 #ifdef MPSBNB_TRACE
 extern "C" int mpsbnb_debug_trace(unsigned long long *out768) {
     return cudaMemcpyFromSymbol(out768, g_trace, sizeof(unsigned long long) * 768) == cudaSuccess ? 0 : -3;
+}
+extern "C" int mpsbnb_debug_waits(unsigned long long *out16, int reset) {
+    if (cudaMemcpyFromSymbol(out16, g_wait, sizeof(unsigned long long) * 16) != cudaSuccess) return -3;
+    if (reset) { unsigned long long z[16] = {0}; cudaMemcpyToSymbol(g_wait, z, sizeof(z)); }
+    return 0;
 }
 #endif
 

@@ -122,7 +122,9 @@ __device__ __forceinline__ void tg_cp_async4(uint32_t dst, const void *src) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
 }
 __device__ __forceinline__ void tg_cp_async16(uint32_t dst, const void *src, uint32_t bytes_valid) {
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes_valid) : "memory");
+    // .cg: L2 only.  x is rewritten between the layers of a stack while, with programmatic dependent launch, this SM's
+    // L1 can still hold the lines the previous layer's kernel read
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes_valid) : "memory");
 }
 // one arrival on `bar` once all asynchronous copies this thread has issued so far have landed
 __device__ __forceinline__ void tg_cp_async_arrive(uint32_t bar) {
@@ -409,12 +411,14 @@ __global__ void __launch_bounds__(TG_THREADS, 1) mpsbnb_decode4_tmem_kernel(cons
             const XT *xr = reinterpret_cast<const XT *>(L->x) + (int64_t)m * L->x_ld;
             if (L->x_vec_ok) {
                 if (k0 >= L->K) return make_uint4(0u, 0u, 0u, 0u);
-                return *reinterpret_cast<const uint4 *>(xr + (k0 % L->x_period));
+                // L2 only: with programmatic dependent launch this SM's L1 may still hold lines of x that the previous
+                // layer's kernel read before the boundary kernel rewrote them
+                return __ldcg(reinterpret_cast<const uint4 *>(xr + (k0 % L->x_period)));
             }
             uint16_t ev[8];
 #pragma unroll
             for (int j = 0; j < 8; ++j)
-                ev[j] = (k0 + j < L->K) ? *reinterpret_cast<const uint16_t *>(xr + (k0 + j) % L->x_period) : (uint16_t)0;
+                ev[j] = (k0 + j < L->K) ? __ldcg(reinterpret_cast<const unsigned short *>(xr + (k0 + j) % L->x_period)) : (unsigned short)0;
             return make_uint4(ev[0] | ((uint32_t)ev[1] << 16), ev[2] | ((uint32_t)ev[3] << 16),
                               ev[4] | ((uint32_t)ev[5] << 16), ev[6] | ((uint32_t)ev[7] << 16));
         };
