@@ -133,15 +133,11 @@ typedef struct mpsbnb_linear4_desc {
                                * (several decoder layers in ONE launch); all 0 for an ordinary group */
 } mpsbnb_linear4_desc;
 
-/* Two kernels implement the M <= 8 decode path.  0 (default): TMA ring, table expansion, dot
- * products (M <= 2) or mma.sync (M <= 8) in the consumer warps.  1: TMA ring, table expansion
- * into tensor memory, tcgen05.mma with fp32 accumulators in tensor memory, stream-K work split,
- * batch up to 32 (a 16-column and a 32-column instance).
- * Selects the kernel used by later mpsbnb_gemv_4bit / mpsbnb_gemv_4bit_group_plan calls of this
- * process (other values: query only) and returns the previous selection.  The environment
- * variable MPSBNB_GEMV_IMPL=tc sets the initial value to 1.  No reference counterpart. */
-int mpsbnb_decode_kernel_select(int which);
-/* Largest batch M a group plan accepts with the kernel selected now (8; 32 for the tcgen05 kernel). */
+/* Two kernels implement the decode path, chosen by the batch alone.  M <= 8: TMA ring, table
+ * expansion, dot products (M <= 2) or mma.sync in the consumer warps.  9 <= M <= 32: TMA ring, table
+ * expansion into tensor memory, tcgen05.mma with fp32 accumulators in tensor memory, stream-K work
+ * split (a 16-column and a 32-column instance).  No reference counterpart. */
+/* Largest batch M a group plan accepts (32). */
 int mpsbnb_gemv_4bit_group_max_m(void);
 
 /* Optional closing step of a grouped launch, run inside the kernel by the CTA that finishes last (so no

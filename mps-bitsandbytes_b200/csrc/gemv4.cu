@@ -417,9 +417,8 @@ extern "C" int mpsbnb_gemv_4bit(const void *x, int x_dtype, int64_t M, const uin
         p.K = 0;
     }
     cudaStream_t st = (cudaStream_t)stream;
-    // batch 9 .. 32 always takes the tcgen05 kernel (1.6 - 1.9 TB/s against 1.0 - 1.4 for the direct-load kernel
-    // below); batch <= 8 takes it only when it has been selected (mpsbnb_decode_kernel_select)
-    if (M <= 32 && K > 0 && aligned16(packed) && (M > 8 || decode_uses_tensor_path()))  // TMA ring + tcgen05
+    // batch 9 .. 32 takes the tensor-memory kernel (1.6 - 1.9 TB/s against 1.0 - 1.4 for the direct-load kernel below)
+    if (M > 8 && M <= 32 && K > 0 && aligned16(packed))       // TMA ring + tcgen05
         return gemv4_tc_single(x, x_dtype, M, packed, absmax, absmax2, N, K, quant_type, bias, y, y_dtype, st);
     if (M <= 8 && K > 0 && aligned16(packed))                  // TMA ring + mma.sync
         return gemv4_stream_single(x, x_dtype, M, packed, absmax, absmax2, N, K, quant_type, bias, y, y_dtype, st);

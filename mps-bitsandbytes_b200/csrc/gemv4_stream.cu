@@ -1033,21 +1033,6 @@ extern "C" int mpsbnb_debug_waits(unsigned long long *out16, int reset) {
 }
 #endif
 
-// 0: TMA ring + mma.sync / dot products (default); 1: TMA ring + tcgen05 with the expanded weights in tensor memory
-static int g_decode_kernel = -1;
-bool decode_uses_tensor_path() {
-    if (g_decode_kernel < 0) {
-        const char *e = getenv("MPSBNB_GEMV_IMPL");
-        g_decode_kernel = (e != nullptr && strcmp(e, "tc") == 0) ? 1 : 0;
-    }
-    return g_decode_kernel == 1;
-}
-int decode_kernel_select(int which) {
-    const int old = decode_uses_tensor_path() ? 1 : 0;
-    if (which == 0 || which == 1) g_decode_kernel = which;
-    return old;
-}
-
 // Single linear, M <= 8 (called from mpsbnb_gemv_4bit).
 int gemv4_stream_single(const void *x, int x_dtype, int64_t M, const uint8_t *packed, const void *absmax,
                         const float *absmax2, int64_t N, int64_t K, int quant_type, const void *bias, void *y,
@@ -1067,8 +1052,8 @@ int gemv4_stream_single(const void *x, int x_dtype, int64_t M, const uint8_t *pa
 
 using namespace mpsbnb;
 
-extern "C" int mpsbnb_decode_kernel_select(int which) { return decode_kernel_select(which); }
-extern "C" int mpsbnb_gemv_4bit_group_max_m(void) { return decode_uses_tensor_path() ? 32 : SG_MAX_M; }
+// batch <= 8: this file's kernel; batch 9 .. 32: the tensor-memory kernel of gemv4_tc.cu
+extern "C" int mpsbnb_gemv_4bit_group_max_m(void) { return 32; }
 
 // ------------------------------------------------------------------------------------------
 // grouped launches: a plan (device memory supplied by the caller) holds the linears and units
@@ -1099,9 +1084,9 @@ extern "C" int mpsbnb_gemv_4bit_group_plan(const mpsbnb_linear4_desc *descs, int
                                            mpsbnb_group_plan *plan_out, void *stream) {
     if (descs == nullptr || n_linears <= 0 || plan_dev == nullptr || plan_out == nullptr) return MPSBNB_ERR_INVALID_ARG;
     if (!is_16bit(x_dtype) || !valid_dtype(y_dtype) || (quant_type != MPSBNB_NF4 && quant_type != MPSBNB_FP4)) return MPSBNB_ERR_INVALID_ARG;
-    if (M <= 0 || M > (decode_uses_tensor_path() ? 32 : SG_MAX_M)) return MPSBNB_ERR_UNSUPPORTED;
+    if (M <= 0 || M > 32) return MPSBNB_ERR_UNSUPPORTED;
     if ((reinterpret_cast<uintptr_t>(plan_dev) & 255) != 0) return MPSBNB_ERR_INVALID_ARG;
-    if (decode_uses_tensor_path())
+    if (M > SG_MAX_M)
         return tc_plan(descs, n_linears, M, x_dtype, y_dtype, quant_type, plan_dev, plan_bytes, plan_out, (cudaStream_t)stream);
     const int chunk = 4;
     const int nu = count_units(descs, n_linears, chunk);

@@ -41,8 +41,5 @@ int tc_plan(const mpsbnb_linear4_desc *descs, int n_linears, int64_t M, int x_dt
 int tc_run(const mpsbnb_group_plan *plan, cudaStream_t st);
 int tc_status_fetch(int *out, bool reset);
 int xchg_status_fetch(int *out, bool reset);   // exchange.cu
-// true when the environment selects the tcgen05 decode kernel (MPSBNB_GEMV_IMPL=tc)
-bool decode_uses_tensor_path();
-int decode_kernel_select(int which);
 
 }  // namespace mpsbnb

@@ -176,14 +176,9 @@ class LayerStack:
         elif M <= 8:
             self._build_plans(M)
         elif M <= 32 and self.mid_batch_tcgen05:
-            # batch 9 .. 32: grouped launches of the tcgen05 decode kernel (its MMAs are 16 or 32 columns wide), one
-            # per layer, with the boundary as its own kernel
-            lib = N.lib()
-            old = lib.mpsbnb_decode_kernel_select(C.c_int(1))
-            try:
-                self._build_plans(M)
-            finally:
-                lib.mpsbnb_decode_kernel_select(C.c_int(old))
+            # batch 9 .. 32: grouped launches of the tensor-memory decode kernel (its MMAs are 16 or 32 columns wide),
+            # one per layer, with the boundary as its own kernel
+            self._build_plans(M)
 
     # ------------------------------------------------------------------ fused exchange (world > 1, batch <= 8)
     def _setup_exchange(self, M: int):

@@ -31,7 +31,10 @@ def test_library_loads_and_exports_every_declared_symbol():
 def test_workspace_size_queries_need_no_gpu():
     lib = _native.lib()
     import ctypes as C
+    # block size 64 runs fused: room for a re-pitched copy of x only; other block sizes expand the weight first
     n = lib.mpsbnb_gemm_4bit_workspace_bytes(C.c_int64(2048), C.c_int64(11008), C.c_int64(4096), C.c_int(64))
+    assert 2048 * 4096 * 2 <= n < 11008 * 4096 * 2
+    n = lib.mpsbnb_gemm_4bit_workspace_bytes(C.c_int64(2048), C.c_int64(11008), C.c_int64(4096), C.c_int(128))
     assert n >= 11008 * 4096 * 2
     assert lib.mpsbnb_gemm_4bit_workspace_bytes(C.c_int64(0), C.c_int64(8), C.c_int64(8), C.c_int(64)) == 0
 

@@ -1,8 +1,6 @@
-"""GPU parity of the two decode kernels (M <= 8) against the oracle: the default one (dot products for
-batch <= 2, mma.sync above) in both activation types, and the tcgen05 one (weights expanded into tensor
-memory), selected through mpsbnb_decode_kernel_select.  Bound: max |y - ref| / max |ref| <= 1e-2."""
-import ctypes as C
-
+"""GPU parity of the two decode kernels against the oracle: the one for batch <= 8 (dot products for
+batch <= 2, mma.sync above) in both activation types, and the one for batch 9 .. 32 (weights expanded into
+tensor memory, tcgen05.mma).  Bound: rel_err <= 1e-2."""
 import numpy as np
 import pytest
 import torch
@@ -15,14 +13,6 @@ from test_gpu_stack import oracle_stack
 
 pytestmark = pytest.mark.gpu
 TOL = 1e-2
-
-
-@pytest.fixture
-def tcgen05_kernel():
-    lib = _native.lib()
-    old = lib.mpsbnb_decode_kernel_select(C.c_int(1))
-    yield
-    lib.mpsbnb_decode_kernel_select(C.c_int(old))
 
 
 def _case(rng, M, N, K, qt, dq, dt):
@@ -46,8 +36,8 @@ def test_default_kernel_both_types(M, dt):
 
 
 @pytest.mark.parametrize("dt", ["float16", "bfloat16"])
-@pytest.mark.parametrize("M", [1, 2, 5, 8, 9, 16, 17, 25, 32])
-def test_tcgen05_kernel_matches_oracle(tcgen05_kernel, M, dt):
+@pytest.mark.parametrize("M", [9, 12, 16, 17, 25, 32])
+def test_tcgen05_kernel_matches_oracle(M, dt):
     rng = np.random.default_rng(200 + M)
     # one stage / many stages / ragged K and N / scale groups that are not 4-aligned (nb = 65) / 33 row tiles
     for (N, K, qt, dq) in [(128, 256, "nf4", False), (200, 1088, "nf4", True), (96, 4104, "fp4", False),
@@ -56,8 +46,8 @@ def test_tcgen05_kernel_matches_oracle(tcgen05_kernel, M, dt):
     assert_device_ok()
 
 
-@pytest.mark.parametrize("M", [1, 4])
-def test_tcgen05_kernel_grouped_stack(tcgen05_kernel, M):
+@pytest.mark.parametrize("M", [9, 20, 32])
+def test_tcgen05_kernel_grouped_stack(M):
     """The grouped launch cuts row tiles between CTAs (fp32 workspace + arrival counters): three layers, graph
     replayed twice, so the workspace has to come back to zero every time."""
     cfg = S.StackConfig("tiny", hidden=256, ffn=704, kv=64, layers=3)
