@@ -168,7 +168,10 @@ typedef struct mpsbnb_group_epilogue {
     int *tile_cnt;
     float alpha;
     int M, hs, H, rank, nranks, mul, add, tile_expect;
-    int nbuf, pad_;           /* buffers peer_h rotates over (0 or 1: a single one) */
+    int nbuf;                 /* buffers peer_h rotates over (0 or 1: a single one) */
+    int count_tiles;          /* streamed closing step: 0 = the CTA that closes the shard's last tile SETS every rank's flag to
+                               * step * mul + add + segment; 1 = every closed tile ADDS 1 to every rank's flag (no counter,
+                               * no second fence: waiters then expect a multiple of the tiles per shard, see wait_seg_mul) */
 } mpsbnb_group_epilogue;
 
 typedef struct mpsbnb_group_plan {
@@ -185,7 +188,9 @@ typedef struct mpsbnb_group_plan {
     const int *wait_step;
     int wait_n, wait_mul, wait_add;
     int acc_parts;            /* filled by the plan call: units per 32-row tile and segment that add into an accumulator */
-    int n_segments, pad_;     /* filled by the plan call */
+    int n_segments;           /* filled by the plan call */
+    int wait_seg_mul;         /* set by the caller: linears of segment g wait for (*wait_step) * wait_mul + wait_add + g * wait_seg_mul
+                               * (0 is read as 1) */
     mpsbnb_group_epilogue ep; /* optional, set by the caller before a run (default kernel only) */
 } mpsbnb_group_plan;
 

@@ -36,7 +36,7 @@ class GroupEpilogue(C.Structure):
     _fields_ = [("acc", C.c_void_p), ("peer_h", C.c_void_p), ("peer_flags", C.c_void_p), ("step", C.c_void_p),
                 ("counter", C.c_void_p), ("tile_cnt", C.c_void_p), ("alpha", C.c_float), ("M", C.c_int), ("hs", C.c_int),
                 ("H", C.c_int), ("rank", C.c_int), ("nranks", C.c_int), ("mul", C.c_int), ("add", C.c_int),
-                ("tile_expect", C.c_int), ("nbuf", C.c_int), ("pad_", C.c_int)]
+                ("tile_expect", C.c_int), ("nbuf", C.c_int), ("count_tiles", C.c_int)]
 
 
 class GroupPlan(C.Structure):
@@ -45,7 +45,7 @@ class GroupPlan(C.Structure):
                 ("M", C.c_int), ("x_dtype", C.c_int), ("quant_type", C.c_int), ("flags", C.c_int),
                 ("aux_offset", C.c_int64), ("grid", C.c_int), ("impl", C.c_int),
                 ("wait_flags", C.c_void_p), ("wait_step", C.c_void_p), ("wait_n", C.c_int), ("wait_mul", C.c_int),
-                ("wait_add", C.c_int), ("acc_parts", C.c_int), ("n_segments", C.c_int), ("pad2_", C.c_int), ("ep", GroupEpilogue)]
+                ("wait_add", C.c_int), ("acc_parts", C.c_int), ("n_segments", C.c_int), ("wait_seg_mul", C.c_int), ("ep", GroupEpilogue)]
 
 
 class NativeLibraryError(RuntimeError):

@@ -103,7 +103,7 @@ struct StreamArgs {
     uint32_t zero;            // always 0; known only at run time (orders the slot release after the loads)
     const int *wait_flags;    // wait_n flags in this GPU's memory that the loaders wait for before the first read of x:
     const int *wait_step;     //   every flag >= (*wait_step) * wait_mul + wait_add  (peers raise them, see exchange.cu)
-    int wait_n, wait_mul, wait_add;
+    int wait_n, wait_mul, wait_add, wait_seg_mul;
     mpsbnb_group_epilogue ep; // closing step by the last CTA (ep.acc == nullptr: none)
     uint32_t sleep_cons;      // ns a consumer warp sleeps between probes of a barrier that is not ready
     uint32_t sleep_other;     // same for the producer, loader and reducer warps
@@ -512,14 +512,17 @@ __global__ void __launch_bounds__(SG_THREADS, 1) mpsbnb_decode4_stream_kernel(co
             __syncwarp();
             if (lane == 0) mbar_arrive(red_empty(buf));
             if (a.ep.tile_cnt != nullptr && L->acc == a.ep.acc && L->acc != nullptr) {
-                // streamed closing step: count this unit's contribution to its 32-row tile.  The count is a release:
-                // it orders this warp's accumulator updates before it.
+                // streamed closing step: count this unit's contribution to its 32-row tile.  The count is a release (it
+                // orders this warp's accumulator updates before it) and an acquire (whoever counts last, and the closer
+                // warp it hands the tile to through the mailbox barrier, see every earlier contribution).
                 __syncwarp();
                 pend_tile = (L->segment << 16) | (un.row0 / SG_ROWS);
+                (void)SG_TIMED(9, ([&]() {
                 if (lane == 0)
-                    asm volatile("atom.add.release.gpu.global.s32 %0, [%1], 1;" : "=r"(pend_old) : "l"(a.ep.tile_cnt + un.row0 / SG_ROWS) : "memory");
+                    asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], 1;" : "=r"(pend_old) : "l"(a.ep.tile_cnt + un.row0 / SG_ROWS) : "memory");
                 // looked at right away: the next unit may belong to a segment that cannot start before this tile is closed
                 resolve_pending();
+                return true; }()));
             }
         }
         resolve_pending();
@@ -532,7 +535,10 @@ __global__ void __launch_bounds__(SG_THREADS, 1) mpsbnb_decode4_stream_kernel(co
             const int nbuf = a.ep.nbuf > 1 ? a.ep.nbuf : 1;
             int mi = 0; uint32_t mph = 0;
             while (!*abort_flag) {
-                if (!mbar_wait_sleep(mail_full(mi), mph, abort_flag, a.sleep_other)) { atomicExch(&g_stream_status, 209); *abort_flag = 1; break; }
+                if (!SG_TIMED(11, mbar_wait_sleep(mail_full(mi), mph, abort_flag, a.sleep_other))) { atomicExch(&g_stream_status, 209); *abort_flag = 1; break; }
+#ifdef MPSBNB_TRACE
+                const long long tclose0 = clock64();
+#endif
                 const int word = (int)lds_u32v(s_mail + 4u * mi);
                 __syncwarp();
                 if (lane == 0) mbar_arrive(mail_empty(mi));
@@ -540,7 +546,6 @@ __global__ void __launch_bounds__(SG_THREADS, 1) mpsbnb_decode4_stream_kernel(co
                 if (word < 0) break;
                 const int seg = word >> 16, tile = word & 0xFFFF;
                 XT *const *peers = all_peers + (nbuf > 1 ? ((seg + 1) % nbuf) * a.ep.nranks : 0);
-                __threadfence();                                 // the contributions were counted with release atomics
                 const int n = tile * SG_ROWS + lane;
                 if (n < a.ep.hs) {
                     for (int m = 0; m < a.M; ++m) {
@@ -552,7 +557,16 @@ __global__ void __launch_bounds__(SG_THREADS, 1) mpsbnb_decode4_stream_kernel(co
                     }
                 }
                 if (lane == 0) a.ep.tile_cnt[tile] = 0;
-                if (a.ep.nranks > 1) __threadfence_system(); else __threadfence();   // the stores before the count
+                if (a.ep.count_tiles) {
+                    // every closed tile adds 1 to this rank's count on every rank.  The addition is a release at system
+                    // scope (the warp barrier makes it cover all lanes' stores) and needs no answer: no counter of this
+                    // GPU, no second fence, no separate flag store on the path to the waiting ranks.
+                    __syncwarp();
+                    if (lane < a.ep.nranks)
+                        asm volatile("red.release.sys.global.add.s32 [%0], 1;" ::"l"(a.ep.peer_flags[lane] + a.ep.rank) : "memory");
+                    MPSBNB_TRACE_SET(2, seg + 1);
+                } else {
+                (void)SG_TIMED(14, ((a.ep.nranks > 1 ? __threadfence_system() : __threadfence()), true));   // the stores before the count
                 __syncwarp();
                 int done = 0;
                 if (lane == 0) done = atomicAdd(a.ep.counter, 1);
@@ -565,6 +579,10 @@ __global__ void __launch_bounds__(SG_THREADS, 1) mpsbnb_decode4_stream_kernel(co
                     if (a.ep.peer_flags != nullptr && lane < a.ep.nranks)
                         asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(a.ep.peer_flags[lane] + a.ep.rank), "r"((*a.ep.step) * a.ep.mul + a.ep.add + seg) : "memory");
                 }
+                }
+#ifdef MPSBNB_TRACE
+                if (blockIdx.x == 0 && lane == 0) { atomicAdd(&g_wait[10], (unsigned long long)(clock64() - tclose0)); atomicAdd(&g_wait[12], 1ull); }
+#endif
             }
         }
     } else if (warp > SG_CONSUMERS) {
@@ -659,7 +677,7 @@ __global__ void __launch_bounds__(SG_THREADS, 1) mpsbnb_decode4_stream_kernel(co
                 if (a.wait_n > 0 && my_L->segment > ready_seg) {
                     // x of this segment is written by closing steps: of the previous launch or segment, on this GPU and,
                     // in the N-sharded stack, on the others.  Wait (bounded) for their flags.
-                    const int expect = (*a.wait_step) * a.wait_mul + a.wait_add + my_L->segment;
+                    const int expect = (*a.wait_step) * a.wait_mul + a.wait_add + my_L->segment * a.wait_seg_mul;
                     bool arrived = true;
                     if (blockIdx.x == 0 && me == 0 && lane == 0) MPSBNB_TRACE_SET(0, my_L->segment);
                     if (lane < a.wait_n) {
@@ -1164,7 +1182,7 @@ extern "C" int mpsbnb_gemv_4bit_group_plan(const mpsbnb_linear4_desc *descs, int
     plan_out->wait_flags = nullptr; plan_out->wait_step = nullptr;
     plan_out->wait_n = plan_out->wait_mul = plan_out->wait_add = 0;
     plan_out->acc_parts = acc_parts;
-    plan_out->n_segments = n_segments; plan_out->pad_ = 0;
+    plan_out->n_segments = n_segments; plan_out->wait_seg_mul = 0;
     memset(&plan_out->ep, 0, sizeof(plan_out->ep));
     return MPSBNB_OK;
 }
@@ -1184,6 +1202,7 @@ extern "C" int mpsbnb_gemv_4bit_group_run(const mpsbnb_group_plan *plan, void *s
         if (plan->wait_flags == nullptr || plan->wait_step == nullptr || plan->wait_n > 32) return MPSBNB_ERR_INVALID_ARG;
         args.wait_flags = plan->wait_flags; args.wait_step = plan->wait_step;
         args.wait_n = plan->wait_n; args.wait_mul = plan->wait_mul; args.wait_add = plan->wait_add;
+        args.wait_seg_mul = plan->wait_seg_mul > 0 ? plan->wait_seg_mul : 1;
     }
     if (plan->ep.acc != nullptr) {
         const mpsbnb_group_epilogue &e = plan->ep;

@@ -811,7 +811,7 @@ int tc_plan(const mpsbnb_linear4_desc *descs, int n_linears, int64_t M, int x_dt
     plan_out->impl = 1;
     plan_out->wait_flags = nullptr; plan_out->wait_step = nullptr;
     plan_out->wait_n = plan_out->wait_mul = plan_out->wait_add = plan_out->acc_parts = 0;
-    plan_out->n_segments = 1; plan_out->pad_ = 0;
+    plan_out->n_segments = 1; plan_out->wait_seg_mul = 0;
     memset(&plan_out->ep, 0, sizeof(plan_out->ep));
     return MPSBNB_OK;
 }

@@ -31,7 +31,8 @@ __global__ void outlier_slot_kernel(const int64_t *__restrict__ idx, int64_t n_o
 
 // One CTA per row of x: row maximum over the main columns (clamped to 1e-8), then every main element is
 // quantised to int8 and expanded again, outlier elements are passed through in the compute type.
-template <typename TX, typename T>
+// ZERO_OUT: outlier columns are written as zeros (the fused path multiplies them separately).
+template <typename TX, typename T, bool ZERO_OUT = false>
 __global__ void __launch_bounds__(256) outlier_x_kernel(const TX *__restrict__ x, int64_t M, int64_t K,
                                                         const int *__restrict__ slot, T *__restrict__ out, int64_t ld) {
     __shared__ float red[8];
@@ -45,7 +46,7 @@ __global__ void __launch_bounds__(256) outlier_x_kernel(const TX *__restrict__ x
         const float s127 = __fdiv_rn(a, 127.0f);
         for (int64_t k = threadIdx.x; k < K; k += blockDim.x) {
             const float v = to_f32<TX>(row[k]);
-            out[m * ld + k] = slot[k] == 0 ? i8_times_rounded_scale<T>(quant_i8(v, f), s127) : from_f32<T>(v);
+            out[m * ld + k] = slot[k] == 0 ? i8_times_rounded_scale<T>(quant_i8(v, f), s127) : (ZERO_OUT ? from_f32<T>(0.0f) : from_f32<T>(v));
         }
     }
 }
@@ -92,6 +93,42 @@ __global__ void __launch_bounds__(256) outlier_w16_kernel(const int8_t *__restri
     }
 }
 
+// y[m, n] += sum_j x[m, idx[j]] * outlier_w[n, j] (+ bias[n]): the 16-bit part of the decomposition, a few dozen
+// columns wide.  One thread per output column n, 16 rows of x per CTA (their outlier values sit in shared memory).
+template <typename TX, typename T, typename TY>
+__global__ void __launch_bounds__(256) outlier_add_kernel(const TX *__restrict__ x, int64_t M, int64_t K,
+                                                          const int64_t *__restrict__ idx, int n_out,
+                                                          const T *__restrict__ ow, const T *__restrict__ bias, int64_t N,
+                                                          TY *__restrict__ y) {
+    extern __shared__ float xs[];                               // [16][n_out]
+    const int64_t m0 = (int64_t)blockIdx.y * 16;
+    const int rows = (int)(M - m0 < 16 ? M - m0 : 16);
+    for (int i = threadIdx.x; i < rows * n_out; i += blockDim.x) {
+        const int r = i / n_out, j = i - r * n_out;
+        const int64_t k = idx[j];
+        // the reference casts x to the compute type before the outlier product
+        xs[i] = (k >= 0 && k < K) ? to_f32<T>(from_f32<T>(to_f32<TX>(x[(m0 + r) * K + k]))) : 0.0f;
+    }
+    __syncthreads();
+    const int64_t n = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (n >= N) return;
+    float acc[16];
+#pragma unroll
+    for (int r = 0; r < 16; ++r) acc[r] = 0.0f;
+    for (int j = 0; j < n_out; ++j) {
+        const float w = to_f32<T>(ow[n * n_out + j]);
+#pragma unroll
+        for (int r = 0; r < 16; ++r) acc[r] = fmaf(xs[r * n_out + j], w, acc[r]);   // rows beyond `rows` read stale, unused values
+    }
+    const float b = bias != nullptr ? to_f32<T>(bias[n]) : 0.0f;
+#pragma unroll
+    for (int r = 0; r < 16; ++r)
+        if (r < rows) {
+            TY *p = y + (m0 + r) * N + n;
+            *p = from_f32<TY>(to_f32<TY>(*p) + to_f32<T>(from_f32<T>(acc[r])) + b);
+        }
+}
+
 static inline unsigned o_grid(int64_t items) {
     const int64_t ctas = (items + 255) / 256, cap = (int64_t)sm_count() * 16;
     return (unsigned)(ctas < 1 ? 1 : (ctas > cap ? cap : ctas));
@@ -133,6 +170,31 @@ extern "C" int mpsbnb_outlier_linear(const void *x, int x_dtype, int64_t M, cons
     }
     const bool vec16 = K % 16 == 0 && aligned16(W);             // slot and the operand live in the 256-byte aligned workspace
     const unsigned xgrid = (unsigned)(M < (int64_t)sm_count() * 8 ? M : (int64_t)sm_count() * 8);
+    if (vec16 && n_outliers <= 512) {
+        // Fused path: the int8 weight is never expanded in memory.  x operand = re-quantised main columns, zeros in the
+        // outlier columns; main product by the fused dequantise-GEMM (row scale / 127 on the accumulator); then the
+        // outlier columns' 16-bit product and the bias are added to y.
+        if (op_dtype == MPSBNB_F16) {
+            MPSBNB_DISPATCH_DTYPE(x_dtype, TX, (outlier_x_kernel<TX, __half, true><<<xgrid, 256, 0, st>>>((const TX *)x, M, K, slot, (__half *)xo, ld)));
+        } else {
+            MPSBNB_DISPATCH_DTYPE(x_dtype, TX, (outlier_x_kernel<TX, __nv_bfloat16, true><<<xgrid, 256, 0, st>>>((const TX *)x, M, K, slot, (__nv_bfloat16 *)xo, ld)));
+        }
+        int rc = check_launch();
+        if (rc != MPSBNB_OK) return rc;
+        const bool tail = n_outliers > 0 || bias != nullptr;
+        rc = gemm_wq(1, xo, ld, op_dtype, M, W, K, nullptr, nullptr, w_scales, 1.0f / 127.0f, 0, N, K, 0, nullptr, y, y_dtype, st);
+        if (rc != MPSBNB_OK || !tail) return rc;
+        const dim3 grid((unsigned)((N + 255) / 256), (unsigned)((M + 15) / 16));
+        const size_t smem = (size_t)16 * (size_t)(n_outliers > 0 ? n_outliers : 1) * sizeof(float);
+#define MPSBNB_OUTLIER_ADD(TX, T, TY) outlier_add_kernel<TX, T, TY><<<grid, 256, smem, st>>>((const TX *)x, M, K, outlier_idx, (int)n_outliers, (const T *)outlier_w, (const T *)bias, N, (TY *)y)
+        if (op_dtype == MPSBNB_F16) {
+            MPSBNB_DISPATCH_DTYPE(x_dtype, TX, MPSBNB_DISPATCH_DTYPE(y_dtype, TY, MPSBNB_OUTLIER_ADD(TX, __half, TY)));
+        } else {
+            MPSBNB_DISPATCH_DTYPE(x_dtype, TX, MPSBNB_DISPATCH_DTYPE(y_dtype, TY, MPSBNB_OUTLIER_ADD(TX, __nv_bfloat16, TY)));
+        }
+#undef MPSBNB_OUTLIER_ADD
+        return check_launch();
+    }
     if (op_dtype == MPSBNB_F16) {
         MPSBNB_DISPATCH_DTYPE(x_dtype, TX, (outlier_x_kernel<TX, __half><<<xgrid, 256, 0, st>>>((const TX *)x, M, K, slot, (__half *)xo, ld)));
         if (vec16) outlier_w16_kernel<__half><<<o_grid(N * K / 16), 256, 0, st>>>(W, w_scales, (const __half *)outlier_w, n_outliers, N, K, slot, (__half *)wo, ld);

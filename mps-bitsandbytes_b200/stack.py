@@ -95,10 +95,13 @@ class LayerStack:
 
     def __init__(self, cfg: StackConfig, device, quant_type: str = "nf4", double_quant: bool = True,
                  layers: Optional[int] = None, rank: int = 0, world: int = 1, seed: int = 1000,
-                 dtype: torch.dtype = torch.float16, group=None, use_pdl: bool = True, fused_exchange: bool = True, boundary: Optional[str] = None, persistent: bool = True, mid_batch_tcgen05: bool = True):
+                 dtype: torch.dtype = torch.float16, group=None, use_pdl: bool = True, fused_exchange: bool = True, boundary: Optional[str] = None, persistent: bool = True, mid_batch_tcgen05: bool = True, emulate_peers: bool = False):
         self.cfg, self.device, self.dtype = cfg, torch.device(device), dtype
         self.layers = cfg.layers if layers is None else layers
         self.rank, self.world, self.group = rank, world, group
+        # timing aid: run ONE rank's shard of a `world`-way split on this GPU alone, every peer pointer aimed at this
+        # GPU's own buffers (the per-GPU work of the sharded stack without NVLink; the result is not the model's)
+        self.emulate_peers = emulate_peers and world > 1
         # programmatic dependent launch between the per-layer kernels (single GPU: no NCCL kernel in between)
         self.use_pdl = use_pdl and world == 1
         # world > 1, batch <= 8: the layer boundary stores its shard of h into every rank's buffer over NVLink and
@@ -196,6 +199,16 @@ class LayerStack:
         self.step_ctr = torch.zeros(1, dtype=torch.int32, device=dev)
         self.h_out = torch.zeros(M, cfg.hidden, dtype=self.dtype, device=dev)
         everyone = [None] * g
+        if self.emulate_peers:
+            base = self._xbuf.data_ptr()
+            one = M * cfg.hidden * esz
+            self._peer_h = [torch.tensor([base + p * one] * g, dtype=torch.int64, device=dev) for p in range(nb)]
+            # the kernels write flag pointer[r] + own rank: aim pointer r at flags[r - rank] so that slot r is raised
+            self._peer_flags = torch.tensor([base + h_bytes + 4 * (r - self.rank) for r in range(g)], dtype=torch.int64, device=dev)
+            self._peer_acks = torch.tensor([base + h_bytes + 256 + 4 * (r - self.rank) for r in range(g)], dtype=torch.int64, device=dev)
+            self._peer_h_all = torch.cat(self._peer_h)
+            torch.cuda.synchronize()
+            return
         if g > 1:
             handle = (C.c_ubyte * 64)()
             off = C.c_int64(0)
@@ -327,8 +340,12 @@ class LayerStack:
         ep.peer_h, ep.nbuf, ep.peer_flags = self._peer_h_all.data_ptr(), self._nbuf, self._peer_flags.data_ptr()
         ep.step, ep.mul, ep.add = self.step_ctr.data_ptr(), L, 1
         ep.tile_cnt, ep.tile_expect = self._tile_cnt.data_ptr(), plan.acc_parts
+        # flags[r] counts the 32-row tiles of h that rank r has closed and stored here since the start (every closed
+        # tile adds 1 on every rank): the input of layer l of step s is complete when every count is (s L + l) T
+        T = self._tiles_per_shard = (cfg.hidden // g + 31) // 32
+        ep.count_tiles = 1
         plan.wait_flags, plan.wait_step = self.flags.data_ptr(), self.step_ctr.data_ptr()
-        plan.wait_n, plan.wait_mul, plan.wait_add = g, L, 0
+        plan.wait_n, plan.wait_mul, plan.wait_add, plan.wait_seg_mul = g, L * T, 0, T
         self._plans = [plan]
 
     def _gemv(self, pr: _Proj, x: torch.Tensor, y: torch.Tensor, M: int):
@@ -354,7 +371,8 @@ class LayerStack:
                                               C.c_int(0), N.stream()), "flags_wait")
             N.check(lib.mpsbnb_gemv_4bit_group_run(C.byref(self._plans[0]), N.stream()), "gemv_4bit_group_run")
             if g > 1:     # ... and every rank's last shard has landed here
-                N.check(lib.mpsbnb_flags_wait(N.ptr(self.flags), C.c_int(g), N.ptr(self.step_ctr), C.c_int(L), C.c_int(L),
+                T = self._tiles_per_shard
+                N.check(lib.mpsbnb_flags_wait(N.ptr(self.flags), C.c_int(g), N.ptr(self.step_ctr), C.c_int(L * T), C.c_int(L * T),
                                               C.c_int(0), N.stream()), "flags_wait")
             self.h_out.copy_(self.hbuf[L % self._nbuf])
             N.check(lib.mpsbnb_counter_add(N.ptr(self.step_ctr), C.c_int(1), N.stream()), "counter_add")
