@@ -94,7 +94,9 @@ struct StreamLinear {
     int segment;              // linears of segment g + 1 read what the closing step of segment g wrote
 };
 
-struct StreamUnit { int lin, row0, s_begin, s_end; };
+// nbv: copy of the linear's count of blocks that hold real k - what the consumer warps need of the linear, so that a
+// unit switch costs them no dependent global load
+struct __align__(16) StreamUnit { int lin, row0, s_begin, s_end, nbv, pad0, pad1, pad2; };
 
 struct StreamArgs {
     const StreamLinear *lins; // device array, or nullptr: use `one`
@@ -424,6 +426,7 @@ __global__ void __launch_bounds__(SG_THREADS, 1) mpsbnb_decode4_stream_kernel(co
         if (a.units != nullptr) return a.units[u];
         StreamUnit un;
         un.lin = 0; un.row0 = u * SG_ROWS; un.s_begin = 0; un.s_end = (a.one.nb + SG_STAGE_BLOCKS - 1) / SG_STAGE_BLOCKS;
+        un.nbv = a.one.nbv; un.pad0 = un.pad1 = un.pad2 = 0;
         return un;
     };
     auto lin_of = [&](int i) -> const StreamLinear * { return a.lins != nullptr ? a.lins + i : &a.one; };
@@ -466,9 +469,9 @@ __global__ void __launch_bounds__(SG_THREADS, 1) mpsbnb_decode4_stream_kernel(co
         const int wrt = lane >> 4;
         pdl_grid_dependency_wait();                              // outputs may still be read by the previous kernel
         int uc = 0;
-        int pend_tile = -1, pend_old = 0;                        // pend_tile: segment << 16 | tile
-        // whoever brought the last contribution of a tile hands the tile to the closer warp (mailbox), which
-        // converts it, stores it into every rank's h and re-arms the accumulator without holding this warp up
+        // every unit that added into the accumulator is handed to the closer warp (mailbox: segment << 16 | tile), which
+        // counts it, and, when it was the tile's last contribution, converts the tile, stores it into every rank's h
+        // and re-arms the accumulator - the round trip of the count never holds this warp up
         int mail_i = 0; uint32_t mail_ph = 0;
         auto post = [&](int tile) {
             if (!mbar_wait_sleep(mail_empty(mail_i), mail_ph ^ 1u, abort_flag, a.sleep_other)) { atomicExch(&g_stream_status, 208); *abort_flag = 1; return; }
@@ -476,16 +479,15 @@ __global__ void __launch_bounds__(SG_THREADS, 1) mpsbnb_decode4_stream_kernel(co
             __syncwarp();
             if (++mail_i == SG_MAIL) { mail_i = 0; mail_ph ^= 1u; }
         };
-        auto resolve_pending = [&]() {
-            if (pend_tile < 0) return;
-            const int old = __shfl_sync(0xffffffffu, pend_old, 0);
-            const int tile = pend_tile;
-            pend_tile = -1;
-            if (old == a.ep.tile_expect - 1) post(tile);
-        };
         for (int u = blockIdx.x; u < a.nunits && !*abort_flag; u += gridDim.x, ++uc) {
             const StreamUnit un = unit_of(u);
             const StreamLinear *L = lin_of(un.lin);
+            // what this unit needs of its linear is fetched before the wait, so that the two dependent global loads
+            // (unit, then linear) pass while the consumers are still working on the unit
+            const int LN = L->N, Ldt = L->y_dtype, Lseg = L->segment;
+            const void *Lbias = L->bias;
+            float *Lacc = L->acc;
+            void *Ly = L->y;
             const int buf = uc & 1;
             if (!SG_TIMED(1, mbar_wait_sleep(red_full(buf), (uint32_t)(uc >> 1) & 1u, abort_flag, a.sleep_other))) { atomicExch(&g_stream_status, 204); *abort_flag = 1; break; }
             const float *red = reinterpret_cast<const float *>(p_generic0 + s_red + buf * SG_RED_BYTES);
@@ -500,32 +502,25 @@ __global__ void __launch_bounds__(SG_THREADS, 1) mpsbnb_decode4_stream_kernel(co
 #pragma unroll
                     for (int k8 = 0; k8 < 8; ++k8) sum += red[((k8 * 2 + wrt) * 8 + m) * 20 + i];
                 }
-                if (n < L->N) {
-                    if (L->bias != nullptr && un.s_begin == 0) sum += to_f32<XT>(reinterpret_cast<const XT *>(L->bias)[n]);
-                    const int64_t o = (int64_t)m * L->N + n;
-                    if (L->acc != nullptr) atomicAdd(L->acc + o, sum);
-                    else if (L->y_dtype == MPSBNB_F16) reinterpret_cast<__half *>(L->y)[o] = __float2half_rn(sum);
-                    else if (L->y_dtype == MPSBNB_BF16) reinterpret_cast<__nv_bfloat16 *>(L->y)[o] = __float2bfloat16_rn(sum);
-                    else reinterpret_cast<float *>(L->y)[o] = sum;
+                if (n < LN) {
+                    if (Lbias != nullptr && un.s_begin == 0) sum += to_f32<XT>(reinterpret_cast<const XT *>(Lbias)[n]);
+                    const int64_t o = (int64_t)m * LN + n;
+                    if (Lacc != nullptr) atomicAdd(Lacc + o, sum);
+                    else if (Ldt == MPSBNB_F16) reinterpret_cast<__half *>(Ly)[o] = __float2half_rn(sum);
+                    else if (Ldt == MPSBNB_BF16) reinterpret_cast<__nv_bfloat16 *>(Ly)[o] = __float2bfloat16_rn(sum);
+                    else reinterpret_cast<float *>(Ly)[o] = sum;
                 }
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(red_empty(buf));
-            if (a.ep.tile_cnt != nullptr && L->acc == a.ep.acc && L->acc != nullptr) {
-                // streamed closing step: count this unit's contribution to its 32-row tile.  The count is a release (it
-                // orders this warp's accumulator updates before it) and an acquire (whoever counts last, and the closer
-                // warp it hands the tile to through the mailbox barrier, see every earlier contribution).
+            if (a.ep.tile_cnt != nullptr && Lacc == a.ep.acc && Lacc != nullptr) {
+                // streamed closing step: the closer warp counts this unit's contribution to its 32-row tile.  The mailbox
+                // barrier (release / acquire inside the CTA) orders this warp's accumulator updates before the closer's
+                // count, which is a release and an acquire at GPU scope.
                 __syncwarp();
-                pend_tile = (L->segment << 16) | (un.row0 / SG_ROWS);
-                (void)SG_TIMED(9, ([&]() {
-                if (lane == 0)
-                    asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], 1;" : "=r"(pend_old) : "l"(a.ep.tile_cnt + un.row0 / SG_ROWS) : "memory");
-                // looked at right away: the next unit may belong to a segment that cannot start before this tile is closed
-                resolve_pending();
-                return true; }()));
+                post((Lseg << 16) | (un.row0 / SG_ROWS));
             }
         }
-        resolve_pending();
         if (a.ep.tile_cnt != nullptr && !*abort_flag) post(-1);    // tells the closer warp that nothing more will come
         __threadfence();                                         // my results before this CTA's arrival at the closing step
     } else if (warp == SG_CONSUMERS + 2 + SG_LOADERS) {
@@ -545,6 +540,13 @@ __global__ void __launch_bounds__(SG_THREADS, 1) mpsbnb_decode4_stream_kernel(co
                 if (++mi == SG_MAIL) { mi = 0; mph ^= 1u; }
                 if (word < 0) break;
                 const int seg = word >> 16, tile = word & 0xFFFF;
+                {
+                    int old = 0;
+                    if (lane == 0)
+                        asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], 1;" : "=r"(old) : "l"(a.ep.tile_cnt + tile) : "memory");
+                    old = __shfl_sync(0xffffffffu, old, 0);
+                    if (old != a.ep.tile_expect - 1) continue;       // not the tile's last contribution
+                }
                 XT *const *peers = all_peers + (nbuf > 1 ? ((seg + 1) % nbuf) * a.ep.nranks : 0);
                 const int n = tile * SG_ROWS + lane;
                 if (n < a.ep.hs) {
@@ -639,7 +641,7 @@ __global__ void __launch_bounds__(SG_THREADS, 1) mpsbnb_decode4_stream_kernel(co
                 }
             };
             int u = blockIdx.x;
-            StreamUnit un = {0, 0, 0, 0};
+            StreamUnit un = {0, 0, 0, 0, 0, 0, 0, 0};
             const StreamLinear *L = nullptr;
             int s = 0, turn = 0, xslot = 0;  // turn: global stage index modulo SG_LOADERS
             uint32_t xph = 0;
@@ -789,14 +791,14 @@ __global__ void __launch_bounds__(SG_THREADS, 1) mpsbnb_decode4_stream_kernel(co
             int nextq = grp;                                          // my next stage in the CTA's stage sequence
             int qb = 0, uc = 0;
             bool ok = true;
-            StreamUnit un = {0, 0, 0, 0};
+            StreamUnit un = {0, 0, 0, 0, 0, 0, 0, 0};
             int u = (int)blockIdx.x;
             if (u < a.nunits) un = unit_of(u);
             while (u < a.nunits && ok && !*abort_flag) {
                 const int un_next = u + (int)gridDim.x;
-                StreamUnit nx = {0, 0, 0, 0};
+                StreamUnit nx = {0, 0, 0, 0, 0, 0, 0, 0};
                 if (un_next < a.nunits) nx = unit_of(un_next);        // in flight while this unit's stages run
-                const int nbv = lin_of(un.lin)->nbv;
+                const int nbv = un.nbv;
                 const int qe = qb + (un.s_end - un.s_begin);
 #pragma unroll 1
                 for (; nextq < qe; nextq += SG_GROUPS) {
@@ -1078,6 +1080,18 @@ extern "C" int mpsbnb_gemv_4bit_group_max_m(void) { return 32; }
 // ------------------------------------------------------------------------------------------
 static inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
+// Stages per unit of a linear that adds into an accumulator (its K is cut so that the tiles of the layer boundary
+// complete early and evenly): 8 when the accumulator has at least one 32-row tile per SM (one GPU holding a whole
+// wide layer: fewer, longer units measured 3 % faster), else 4 (N-sharded: 8 was 12 % slower on an 8-way shard).
+static int sg_chunk(const mpsbnb_linear4_desc *d, int n) {
+    int64_t min_tiles = -1;
+    for (int i = 0; i < n; ++i)
+        if (d[i].acc != nullptr) {
+            const int64_t t = (d[i].N + SG_ROWS - 1) / SG_ROWS;
+            if (min_tiles < 0 || t < min_tiles) min_tiles = t;
+        }
+    return (min_tiles >= sm_count()) ? 8 : 4;
+}
 static int count_units(const mpsbnb_linear4_desc *d, int n, int chunk_stages) {
     int64_t total = 0;
     for (int i = 0; i < n; ++i) {
@@ -1090,7 +1104,7 @@ static int count_units(const mpsbnb_linear4_desc *d, int n, int chunk_stages) {
 
 extern "C" size_t mpsbnb_gemv_4bit_group_plan_bytes(const mpsbnb_linear4_desc *descs, int n_linears) {
     if (descs == nullptr || n_linears <= 0) return 0;
-    const int nu = count_units(descs, n_linears, 4);
+    const int nu = count_units(descs, n_linears, 4);            // the smaller chunk gives the larger plan
     if (nu < 0) return 0;
     const size_t mine = align_up(sizeof(StreamLinear) * (size_t)n_linears, 256) + align_up(sizeof(StreamUnit) * (size_t)nu, 256);
     const size_t other = tc_plan_bytes(descs, n_linears);
@@ -1106,7 +1120,7 @@ extern "C" int mpsbnb_gemv_4bit_group_plan(const mpsbnb_linear4_desc *descs, int
     if ((reinterpret_cast<uintptr_t>(plan_dev) & 255) != 0) return MPSBNB_ERR_INVALID_ARG;
     if (M > SG_MAX_M)
         return tc_plan(descs, n_linears, M, x_dtype, y_dtype, quant_type, plan_dev, plan_bytes, plan_out, (cudaStream_t)stream);
-    const int chunk = 4;
+    const int chunk = sg_chunk(descs, n_linears);
     const int nu = count_units(descs, n_linears, chunk);
     if (nu <= 0) return MPSBNB_ERR_INVALID_ARG;
     const size_t lin_bytes = align_up(sizeof(StreamLinear) * (size_t)n_linears, 256);
@@ -1154,7 +1168,7 @@ extern "C" int mpsbnb_gemv_4bit_group_plan(const mpsbnb_linear4_desc *descs, int
                     const int s1 = s0 + step < S ? s0 + step : S;
                     const int len = s1 - s0 > chunk * 8 ? chunk * 8 : s1 - s0;
                     if (len != pass) continue;
-                    for (int r0 = 0; r0 < lins[i].N; r0 += SG_ROWS) units[nu2++] = StreamUnit{i, r0, s0, s1};
+                    for (int r0 = 0; r0 < lins[i].N; r0 += SG_ROWS) units[nu2++] = StreamUnit{i, r0, s0, s1, lins[i].nbv, 0, 0, 0};
                 }
             }
         }
