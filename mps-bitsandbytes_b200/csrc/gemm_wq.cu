@@ -44,7 +44,17 @@ using namespace sm100;
 
 constexpr int WQ_GROUPS = 2;                 // expander groups; group g takes the K steps kb = g (mod 2)
 constexpr int WQ_GROUP_WARPS = 8;
-constexpr int WQ_THREADS = (7 + WQ_GROUPS * WQ_GROUP_WARPS) * 32;
+// Warp schedulers take warps by (warp index mod 4).  The MMA issuer is warp 1, and its loop is the serial path of the
+// kernel, so no expander warp may share its scheduler: expanders are the warps from 7 on whose index is not 1 mod 4; the
+// warps in between (9, 13, 17, 21, 25) do nothing.
+constexpr int WQ_FIRST_EXPANDER = 7;
+constexpr int WQ_WARPS = 28;
+constexpr int WQ_THREADS = WQ_WARPS * 32;
+__host__ __device__ constexpr int wq_expander_index(int warp) {      // 0 .. 15, or -1
+    return (warp < WQ_FIRST_EXPANDER || (warp & 3) == 1) ? -1 : warp - WQ_FIRST_EXPANDER - (warp >= 9 ? (warp - 9) / 4 + 1 : 0);
+}
+static_assert(wq_expander_index(7) == 0 && wq_expander_index(8) == 1 && wq_expander_index(10) == 2 && wq_expander_index(27) == 15 &&
+              wq_expander_index(9) == -1 && wq_expander_index(25) == -1, "sixteen expander warps");
 constexpr int WQ_ROWS = 128;                 // weight rows per tile (MMA M)
 constexpr int WQ_BK = 64;                    // k per MMA stage
 constexpr int WQ_WS = 4;                     // W stages (expanded operand tiles, 16 KB each)
@@ -184,9 +194,9 @@ mpsbnb_gemm_wq_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_con
         tmem_alloc(smem_u32((const void *)tmem_slot), 2 * TM);
         tmem_relinquish();
     }
-    if (MODE == WQ_4BIT && warp >= 7 && warp < 15) {
+    if (MODE == WQ_4BIT && wq_expander_index(warp) >= 0 && wq_expander_index(warp) < 8) {
         // byte -> (code[low nibble], code[high nibble]) as an fp16 pair, one replica per lane
-        const int w7 = warp - 7;
+        const int w7 = wq_expander_index(warp);
         const float my_code = kCode[a.quant_type][lane & 15];
         const int byte = w7 * 32 + lane;
         const float lo = __shfl_sync(0xffffffffu, my_code, byte & 15);
@@ -320,12 +330,12 @@ mpsbnb_gemm_wq_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_con
             if (lane == 0) mbar_arrive(tempty(acc));
             if (++acc == 2) { acc = 0; acc_phase ^= 1; }
         }
-    } else {
-        // ------------------------------------------------------------ expanders (warps 7..22)
+    } else if (wq_expander_index(warp) >= 0) {
+        // ------------------------------------------------------------ expanders (sixteen of the warps 7..27)
         // Two groups of eight warps; group g expands the K steps kb = g, g + 2, ... of every tile, alternating between
         // two W stages of its own, so that it can fill one while the tensor core still reads the other.  Thread
         // (r, h) of a group owns half a weight row of the stage (32 k): 16 packed bytes in, 64 bytes out.
-        const int ew = warp - 7;
+        const int ew = wq_expander_index(warp);
         const int grp = ew / WQ_GROUP_WARPS;
         // lanes 0-15 of a warp take the first half (h = 0) of sixteen consecutive rows, lanes 16-31 the second: eight
         // consecutive lanes then touch eight different 16-byte columns of the swizzled tiles (no bank conflicts)

@@ -172,3 +172,44 @@ def test_int8_and_fp8_matmuls(golden):
     y = bnb.matmul_fp8_e4m3(torch.from_numpy(x).cuda(), torch.from_numpy(c8).cuda(), torch.from_numpy(s8).cuda())
     assert rel_err(to_np(y), O.matmul_fp8_e4m3(x, c8, s8)) <= TOL
     assert_device_ok()
+
+
+def test_short_argument_tensors_raise_instead_of_reading_out_of_bounds():
+    """The kernels take raw pointers: tensors shorter than the shapes imply are refused on the host."""
+    rng = np.random.default_rng(9)
+    packed, st, _ = quantized(rng, 64, 200, "nf4", True)           # K = 200: rows are padded to 256 in the layout
+    x = torch.randn(3, 200, device="cuda", dtype=torch.float16)
+    with pytest.raises(ValueError, match="packed weight"):
+        bnb.matmul_4bit(x, packed[:-8], st)
+    with pytest.raises(ValueError, match="bias"):
+        bnb.matmul_4bit(x, packed, st, torch.zeros(63, device="cuda", dtype=torch.float16))
+    short = bnb.QuantState(absmax=st.absmax[:-1], shape=st.shape, blocksize=64, quant_type="nf4", dtype=st.dtype, state2=st.state2)
+    with pytest.raises(ValueError, match="absmax"):
+        bnb.matmul_4bit(x, packed, short)
+    # a packed tensor stored in another integer type holds the byte VALUES and is converted back
+    y = bnb.matmul_4bit(x, packed, st)
+    assert torch.equal(bnb.matmul_4bit(x, packed.to(torch.int32), st), y)
+    q = torch.zeros(8, 32, dtype=torch.int8, device="cuda")
+    with pytest.raises(ValueError, match="scales"):
+        bnb.dequantize_rowwise(q, torch.ones(7, device="cuda"))
+    with pytest.raises(ValueError, match="scales"):
+        bnb.dequantize_fp8_e4m3(q.view(torch.uint8), torch.ones(7, device="cuda"))
+    with pytest.raises(ValueError, match="col_scales"):
+        bnb.dequantize_colrow(q, torch.ones(8, device="cuda"), torch.ones(31, device="cuda"))
+    with pytest.raises(ValueError, match="B_scales"):
+        bnb.matmul_int8(q, torch.zeros(32, 16, dtype=torch.int8, device="cuda"), torch.ones(8, device="cuda"), torch.ones(15, device="cuda"))
+    with pytest.raises(ValueError, match="weight_row_scales"):
+        bnb.matmul_colrow(torch.zeros(2, 32, device="cuda", dtype=torch.float16), q, torch.ones(7, device="cuda"), torch.ones(32, device="cuda"))
+    with pytest.raises(ValueError, match="weight_scales"):
+        bnb.matmul_fp8_e4m3(torch.zeros(2, 32, device="cuda", dtype=torch.float16), q.view(torch.uint8), torch.ones(7, device="cuda"))
+    with pytest.raises(ValueError, match="row_stats"):
+        bnb.double_quant(torch.zeros(8, 32, device="cuda"), row_stats=torch.ones(7, device="cuda"))
+    with pytest.raises(ValueError, match="absmax"):
+        bnb.quantize_blockwise(torch.zeros(1000, device="cuda"), absmax=torch.ones(1, device="cuda"), blocksize=256)
+    # dequant_absmax (tensor form) runs on a kernel
+    aq = torch.randint(-127, 128, (3, 600), dtype=torch.int8, device="cuda")
+    sc = torch.rand(3, 3, device="cuda") + 0.5
+    ref = aq.float() * sc[:, torch.arange(600, device="cuda") // 256]
+    assert torch.equal(bnb.dequant_absmax(aq, sc, 256), ref)
+    assert torch.equal(bnb.dequant_absmax(aq[0], sc[0], 256), ref[0])
+    assert_device_ok()
