@@ -268,7 +268,9 @@ template <> struct StageOps<__nv_bfloat16> {
 // reads the 32 packed bytes of its row for one block, looks every byte up (same byte-permute + table load)
 // and multiplies the two codes with the two x values by mixed-precision FMAs (fp16 x fp16 + fp32 -> fp32,
 // exact products, fp32 accumulation).  x is the same for all lanes, so its loads are broadcasts.
-constexpr int SG_DOT_MAX_M = 2;
+constexpr int SG_DOT_MAX_M = 2;                          // array bound of the dot path (it can do two batch rows)
+constexpr int SG_DOT_RUN_M = 1;                          // ... and the batch up to which it runs: at batch 2 the MMA path
+                                                         // measured 11 % faster (3317 against 3003 GB/s on the 70B-shaped stack)
 __device__ __forceinline__ uint4 lds128v(uint32_t addr) {
     uint4 v;
     asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
@@ -494,7 +496,7 @@ __global__ void __launch_bounds__(SG_THREADS, 1) mpsbnb_decode4_stream_kernel(co
             const int n = un.row0 + lane;
             for (int m = 0; m < a.M; ++m) {
                 float sum = 0.0f;
-                if (a.M <= SG_DOT_MAX_M) {
+                if (a.M <= SG_DOT_RUN_M) {
                     // dot-product path: [warp][m][row] partial sums of all 16 warps
 #pragma unroll
                     for (int w16 = 0; w16 < SG_CONSUMERS; ++w16) sum += red[(w16 * SG_DOT_MAX_M + m) * 32 + lane];
@@ -769,7 +771,7 @@ __global__ void __launch_bounds__(SG_THREADS, 1) mpsbnb_decode4_stream_kernel(co
         constexpr uint32_t ITEM_W = (uint32_t)(KG_STEP * 2 * 1024);   // 2 blocks = half a 4 KiB box
         constexpr uint32_t ITEM_X = (uint32_t)(KG_STEP * 2 * 64 * 2); // x bytes per block pair step
         constexpr uint32_t ITEM_A = (uint32_t)(KG_STEP * 2 * 32 * 4); // scale bytes per block pair step
-        const bool dot = a.M <= SG_DOT_MAX_M;                    // lane = row, one block per item (see dot_block)
+        const bool dot = a.M <= SG_DOT_RUN_M;                     // lane = row, one block per item (see dot_block)
         if (dot) {
             woff[0] = (uint32_t)(lane * 128 + (((2 * j) ^ (lane & 7)) << 4));
             woff[1] = (uint32_t)(lane * 128 + (((2 * j + 1) ^ (lane & 7)) << 4));
