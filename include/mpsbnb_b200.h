@@ -171,7 +171,10 @@ typedef struct mpsbnb_group_epilogue {
     int nbuf;                 /* buffers peer_h rotates over (0 or 1: a single one) */
     int count_tiles;          /* streamed closing step: 0 = the CTA that closes the shard's last tile SETS every rank's flag to
                                * step * mul + add + segment; 1 = every closed tile ADDS 1 to every rank's flag (no counter,
-                               * no second fence: waiters then expect a multiple of the tiles per shard, see wait_seg_mul) */
+                               * no second fence: waiters then expect a multiple of the tiles per shard, see wait_seg_mul);
+                               * 2 = no flags at all: peer_h are TAGGED buffers (8-byte entries {two values, tag}, tag =
+                               * step * mul + add + segment) and every linear of the plan reads its x in that form, expecting
+                               * the tag (*wait_step) * wait_mul + wait_add + segment * wait_seg_mul */
 } mpsbnb_group_epilogue;
 
 typedef struct mpsbnb_group_plan {
@@ -243,6 +246,13 @@ int mpsbnb_stack_boundary_push(float *acc, float alpha, int64_t M, int64_t hs, i
 int mpsbnb_flags_wait(const int *flags, int n, const int *step, int mul, int add, int pdl, void *stream);
 int mpsbnb_flags_push(int *const *peer_flags, int rank, int nranks, const int *step, int mul, int add, void *stream);
 int mpsbnb_counter_add(int *counter, int value, void *stream);
+/* Tagged form of a 16-bit matrix [M, H] (H even): 8-byte entries {columns 2p and 2p+1, tag}, what the decode kernel's
+ * closing step exchanges when ep.count_tiles == 2 (an aligned 8-byte store arrives whole, so a reader that sees the tag has
+ * the data: no fence, no flag).  mpsbnb_tagged_write converts a plain matrix with tag (*step) * mul + add (a stack's input);
+ * mpsbnb_tagged_read waits - bounded, then device status 502 - until every entry carries that tag and returns the plain
+ * matrix (a stack's result).  No reference counterpart. */
+int mpsbnb_tagged_write(const void *x, int64_t M, int64_t H, void *tagged, const int *step, int mul, int add, void *stream);
+int mpsbnb_tagged_read(const void *tagged, int64_t M, int64_t H, void *out, const int *step, int mul, int add, void *stream);
 
 /* Multi-GPU form of the boundary: G[r][m][c] holds the all-gathered per-rank shards of the
  * new h (c < H / nranks); writes h[m, r*H/nranks + c] = G[r][m][c] and e as above.

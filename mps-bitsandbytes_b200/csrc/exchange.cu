@@ -82,6 +82,36 @@ __global__ void flags_push_kernel(int *const *peer_flags, int rank, int nranks, 
     if ((int)threadIdx.x < nranks) st_release_sys(peer_flags[threadIdx.x] + rank, (*step) * mul + add);
 }
 
+// Tagged form of a 16-bit matrix [M, H]: entry p of row m = {columns 2 p and 2 p + 1, tag} in 8 bytes (see the closer
+// warp of the decode kernel).  ll_write puts a plain matrix into that form with tag (*step) * mul + add.
+__global__ void ll_write_kernel(const uint32_t *__restrict__ x, int64_t npairs, unsigned long long *__restrict__ dst,
+                                const int *step, int mul, int add) {
+    sm100::pdl_launch_dependents();
+    sm100::pdl_grid_dependency_wait();
+    const unsigned long long tag = (unsigned long long)(uint32_t)((*step) * mul + add) << 32;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < npairs; i += (int64_t)gridDim.x * blockDim.x)
+        asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(dst + i), "l"(tag | x[i]) : "memory");
+}
+
+// The reverse, for a matrix that other GPUs are still writing: every entry is read until it carries the expected tag
+// (bounded: about a second, then status 502), then its two values are stored.
+__global__ void ll_read_kernel(const unsigned long long *__restrict__ src, int64_t npairs, uint32_t *__restrict__ out,
+                               const int *step, int mul, int add) {
+    sm100::pdl_launch_dependents();
+    sm100::pdl_grid_dependency_wait();
+    const uint32_t expect = (uint32_t)((*step) * mul + add);
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < npairs; i += (int64_t)gridDim.x * blockDim.x) {
+        unsigned long long v;
+        const long long t0 = clock64();
+        for (;;) {
+            asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(src + i) : "memory");
+            if ((uint32_t)(v >> 32) == expect) break;
+            if (clock64() - t0 > 2000000000ll) { atomicExch(&g_xchg_status, 502); break; }
+        }
+        out[i] = (uint32_t)v;
+    }
+}
+
 __global__ void counter_add_kernel(int *ctr, int v) {
     sm100::pdl_launch_dependents();
     sm100::pdl_grid_dependency_wait();
@@ -178,6 +208,22 @@ extern "C" int mpsbnb_flags_wait(const int *flags, int n, const int *step, int m
 extern "C" int mpsbnb_flags_push(int *const *peer_flags, int rank, int nranks, const int *step, int mul, int add, void *stream) {
     if (peer_flags == nullptr || step == nullptr || nranks <= 0 || nranks > 32 || rank < 0 || rank >= nranks) return MPSBNB_ERR_INVALID_ARG;
     flags_push_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(peer_flags, rank, nranks, step, mul, add);
+    return check_launch();
+}
+
+extern "C" int mpsbnb_tagged_write(const void *x, int64_t M, int64_t H, void *tagged, const int *step, int mul, int add, void *stream) {
+    if (x == nullptr || tagged == nullptr || step == nullptr || M <= 0 || H <= 0 || H % 2 != 0) return MPSBNB_ERR_INVALID_ARG;
+    const int64_t n = M * H / 2;
+    ll_write_kernel<<<(unsigned)((n + 255) / 256 < 296 ? (n + 255) / 256 : 296), 256, 0, (cudaStream_t)stream>>>(
+        (const uint32_t *)x, n, (unsigned long long *)tagged, step, mul, add);
+    return check_launch();
+}
+
+extern "C" int mpsbnb_tagged_read(const void *tagged, int64_t M, int64_t H, void *out, const int *step, int mul, int add, void *stream) {
+    if (out == nullptr || tagged == nullptr || step == nullptr || M <= 0 || H <= 0 || H % 2 != 0) return MPSBNB_ERR_INVALID_ARG;
+    const int64_t n = M * H / 2;
+    ll_read_kernel<<<(unsigned)((n + 255) / 256 < 296 ? (n + 255) / 256 : 296), 256, 0, (cudaStream_t)stream>>>(
+        (const unsigned long long *)tagged, n, (uint32_t *)out, step, mul, add);
     return check_launch();
 }
 

@@ -106,6 +106,7 @@ struct StreamArgs {
     const int *wait_flags;    // wait_n flags in this GPU's memory that the loaders wait for before the first read of x:
     const int *wait_step;     //   every flag >= (*wait_step) * wait_mul + wait_add  (peers raise them, see exchange.cu)
     int wait_n, wait_mul, wait_add, wait_seg_mul;
+    int x_ll;                 // x of every linear is in tagged form: 8-byte entries {two 16-bit values, tag} (see the closer warp)
     mpsbnb_group_epilogue ep; // closing step by the last CTA (ep.acc == nullptr: none)
     uint32_t sleep_cons;      // ns a consumer warp sleeps between probes of a barrier that is not ready
     uint32_t sleep_other;     // same for the producer, loader and reducer warps
@@ -368,8 +369,12 @@ __global__ void __launch_bounds__(SG_THREADS, 1) mpsbnb_decode4_stream_kernel(co
     auto mail_empty = [&](int i) { return s_bar + 352u + 8u * (SG_MAIL + i); };
     const uint32_t s_mail = s_bar + 416u;
     const uint32_t s_xs = (s_bar + 512u + 127u) & ~127u;
+    // tagged x, batch 1: a staging buffer per loader warp for one stage's entries (1024 columns = 512 entries of 8 bytes), filled by bulk copies
+    const uint32_t s_stage = s_xs + (uint32_t)nxs * xs_bytes;
+    const uint32_t stage_bytes = (a.x_ll && a.M == 1) ? (uint32_t)SG_LOADERS * 4096u : 0u;
+    auto sfull_bar = [&](int i) { return s_bar + 448u + 8u * i; };
     SlotMap sm;
-    sm.low0 = (s_xs + (uint32_t)nxs * xs_bytes + 1023u) & ~1023u;
+    sm.low0 = (s_stage + stage_bytes + 1023u) & ~1023u;
     sm.high0 = SG_HIGH_ABS;
     sm.nlow = (int)((SG_LUT_ABS - sm.low0) / SG_W_BYTES);
     {
@@ -399,6 +404,7 @@ __global__ void __launch_bounds__(SG_THREADS, 1) mpsbnb_decode4_stream_kernel(co
         for (int s = 0; s < nslots; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), SG_GROUP_WARPS); }
         for (int b = 0; b < 2; ++b) { mbar_init(red_full(b), SG_CONSUMERS); mbar_init(red_empty(b), 1); }
         for (int i = 0; i < SG_MAIL; ++i) { mbar_init(mail_full(i), 1); mbar_init(mail_empty(i), 1); }
+        for (int i = 0; i < SG_LOADERS; ++i) mbar_init(sfull_bar(i), 1);
         for (int s = 0; s < nxs; ++s) { mbar_init(xfull_bar(s), 1); mbar_init(xempty_bar(s), SG_GROUP_WARPS); }
         *abort_flag = 0;
         fence_mbar_init();
@@ -544,10 +550,34 @@ __global__ void __launch_bounds__(SG_THREADS, 1) mpsbnb_decode4_stream_kernel(co
                 const int seg = word >> 16, tile = word & 0xFFFF;
                 {
                     int old = 0;
+                    // counts 0 .. expect - 1 and wraps to 0 by itself: the count needs no re-arming store
                     if (lane == 0)
-                        asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], 1;" : "=r"(old) : "l"(a.ep.tile_cnt + tile) : "memory");
+                        asm volatile("atom.inc.acq_rel.gpu.global.u32 %0, [%1], %2;" : "=r"(old) : "l"(a.ep.tile_cnt + tile), "r"(a.ep.tile_expect - 1) : "memory");
                     old = __shfl_sync(0xffffffffu, old, 0);
                     if (old != a.ep.tile_expect - 1) continue;       // not the tile's last contribution
+                }
+                if (a.ep.count_tiles == 2) {
+                    // Tagged exchange: column pair (2 p, 2 p + 1) of h travels as ONE 8-byte store {two 16-bit values, tag}
+                    // with tag = step * L + layer of the consumer, into every rank's buffer.  An aligned 8-byte store
+                    // arrives whole, so a reader that sees the tag has the data: no fence, no count, no flag, and the
+                    // accumulator is read and re-armed by one atomic exchange per element.
+                    unsigned long long *const *peers_ll = reinterpret_cast<unsigned long long *const *>(a.ep.peer_h) +
+                                                          (nbuf > 1 ? ((seg + 1) % nbuf) * a.ep.nranks : 0);
+                    const uint32_t tag = (uint32_t)((*a.ep.step) * a.ep.mul + a.ep.add + seg);
+                    const int c = tile * SG_ROWS + lane;
+                    for (int m = 0; m < a.M; ++m) {
+                        float v = 0.0f;
+                        if (c < a.ep.hs) v = atomicExch(a.ep.acc + (int64_t)m * a.ep.hs + c, 0.0f);
+                        const float vn = __shfl_down_sync(0xffffffffu, v, 1);
+                        if ((lane & 1) == 0 && c < a.ep.hs) {
+                            const unsigned long long w = ((unsigned long long)tag << 32) | pair_bits<XT>(a.ep.alpha * v, a.ep.alpha * vn);
+                            const int64_t o = ((int64_t)m * a.ep.H + (int64_t)a.ep.rank * a.ep.hs + c) >> 1;
+                            for (int r = 0; r < a.ep.nranks; ++r)
+                                asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(peers_ll[r] + o), "l"(w) : "memory");
+                        }
+                    }
+                    MPSBNB_TRACE_SET(2, seg + 1);
+                    continue;
                 }
                 XT *const *peers = all_peers + (nbuf > 1 ? ((seg + 1) % nbuf) * a.ep.nranks : 0);
                 const int n = tile * SG_ROWS + lane;
@@ -560,7 +590,6 @@ __global__ void __launch_bounds__(SG_THREADS, 1) mpsbnb_decode4_stream_kernel(co
                         for (int r = 0; r < a.ep.nranks; ++r) peers[r][o] = hv;
                     }
                 }
-                if (lane == 0) a.ep.tile_cnt[tile] = 0;
                 if (a.ep.count_tiles) {
                     // every closed tile adds 1 to this rank's count on every rank.  The addition is a release at system
                     // scope (the warp barrier makes it cover all lanes' stores) and needs no answer: no counter of this
@@ -666,12 +695,30 @@ __global__ void __launch_bounds__(SG_THREADS, 1) mpsbnb_decode4_stream_kernel(co
             };
             float cur[16];
             int ready_seg = -1;                  // segments whose input is known to be complete
+            // tagged x: whether the stage under the cursor was requested into this warp's staging buffer (a bulk copy needs a
+            // 16-byte aligned source and size - four columns per 16 bytes - in one run, and there is one buffer: batch 1)
+            bool req = false;
+            uint32_t sph = 0;                    // the phase the staging buffer completes next
+            auto request_x = [&]() {
+                req = false;
+                if (stage_bytes == 0u) return;
+                int xc = L->K - s * (SG_STAGE_BLOCKS * 64);
+                xc = xc > SG_STAGE_BLOCKS * 64 ? SG_STAGE_BLOCKS * 64 : xc;
+                const int col0 = (s * (SG_STAGE_BLOCKS * 64)) % L->x_period;
+                if (xc <= 0 || (xc & 3) != 0 || (col0 & 3) != 0 || col0 + xc > L->x_period || (reinterpret_cast<uintptr_t>(L->x) & 15) != 0) return;
+                req = true;
+                if (lane == 0) {
+                    mbar_arrive_expect_tx(sfull_bar(me), (uint32_t)(xc >> 1) * 8u);
+                    bulk_load_1d(s_stage + (uint32_t)me * 4096u, reinterpret_cast<const unsigned long long *>(L->x) + (col0 >> 1), (uint32_t)(xc >> 1) * 8u, sfull_bar(me));
+                }
+            };
             bool more = advance_to_mine();
-            if (more) read_scales(L, un.row0, s, cur);
+            if (more) { read_scales(L, un.row0, s, cur); if (a.x_ll) request_x(); }
             while (more && !*abort_flag) {
                 const int my_x = xslot, my_s = s;
                 const uint32_t my_ph = xph;
                 const StreamLinear *my_L = L;
+                const bool my_req = req;
                 step();
                 float nxt[16];
                 more = advance_to_mine();
@@ -704,7 +751,76 @@ __global__ void __launch_bounds__(SG_THREADS, 1) mpsbnb_decode4_stream_kernel(co
                 for (int j = 0; j < 16; ++j) sts_f32(xb + (j * 32 + lane) * 4, cur[j]);
                 int xcols = my_L->K - my_s * (SG_STAGE_BLOCKS * 64);
                 xcols = xcols > SG_STAGE_BLOCKS * 64 ? SG_STAGE_BLOCKS * 64 : (xcols < 0 ? 0 : xcols);
-                if (my_L->x_bulk_ok) {
+                if (a.x_ll) {
+                    // x in tagged form, written by closer warps here or on other GPUs: 8-byte entries {two values, tag}.  Seeing the
+                    // expected tag IS having the data (an aligned 8-byte store arrives whole): no flag, fence or acquire is
+                    // involved, an entry that does not carry the tag yet is read again (bounded).
+                    const uint32_t expect = (uint32_t)((*a.wait_step) * a.wait_mul + a.wait_add + my_L->segment * a.wait_seg_mul);
+                    const int k_base = my_s * (SG_STAGE_BLOCKS * 64);
+                    const unsigned long long *x2 = reinterpret_cast<const unsigned long long *>(my_L->x);
+                    bool ok = true;
+                    if (my_req) {
+                        // this stage's entries were requested into the warp's staging buffer when the previous one had been
+                        // examined (a loader's stages lie SG_LOADERS apart: the round trip to L2 is long over)
+                        const uint32_t sb = s_stage + (uint32_t)me * 4096u;
+                        const int npairs = xcols >> 1;
+                        long long t0 = 0;
+                        for (;;) {
+                            if (!SG_TIMED(13, mbar_wait_sleep(sfull_bar(me), sph, abort_flag, a.sleep_other))) { atomicExch(&g_stream_status, 210); ok = false; break; }
+                            sph ^= 1u;
+                            bool good = true;
+                            // 16-byte chunks (two entries) c = lane + 32 j; four loads are issued before the first value is looked at
+#pragma unroll
+                            for (int h = 0; h < 2; ++h) {
+                                uint32_t r[4][4];
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) {
+                                    const int c = lane + 32 * (4 * h + j);
+                                    if (2 * c < npairs)
+                                        asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(r[j][0]), "=r"(r[j][1]), "=r"(r[j][2]), "=r"(r[j][3]) : "r"(sb + (uint32_t)c * 16u));
+                                    else { r[j][1] = expect; r[j][3] = expect; r[j][0] = 0u; r[j][2] = 0u; }
+                                }
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) {
+                                    const int c = lane + 32 * (4 * h + j);
+                                    good = good && r[j][1] == expect && r[j][3] == expect;
+                                    if (2 * c < npairs)                           // K is a multiple of 4 here: no column beyond it
+                                        asm volatile("st.shared.v2.u32 [%0], {%1, %2};" :: "r"(xb + (uint32_t)SG_A_BYTES + (uint32_t)c * 8u), "r"(r[j][0]), "r"(r[j][2]) : "memory");
+                                }
+                            }
+                            if (__all_sync(0xffffffffu, good)) break;
+                            if (t0 == 0) t0 = clock64();
+                            if (*abort_flag != 0 || clock64() - t0 > 2000000000ll) { atomicExch(&g_stream_status, 207); ok = false; break; }
+                            if (lane == 0) {                                      // some entry is not there yet: fetch the row again
+                                mbar_arrive_expect_tx(sfull_bar(me), (uint32_t)npairs * 8u);
+                                bulk_load_1d(sb, x2 + (((my_s * (SG_STAGE_BLOCKS * 64)) % my_L->x_period) >> 1), (uint32_t)npairs * 8u, sfull_bar(me));
+                            }
+                            __syncwarp();
+                        }
+                    } else {
+                        // a batch above 1, a stage that straddles the period, an odd offset: the entries are read where they lie
+                        const int npairs = (xcols + 1) >> 1;
+                        for (int m = 0; m < a.M; ++m)
+                            for (int i = lane; i < npairs; i += 32) {
+                                const unsigned long long *p = x2 + (int64_t)m * (my_L->x_ld >> 1) + (((k_base + 2 * i) % my_L->x_period) >> 1);
+                                unsigned long long v;
+                                const long long t0 = clock64();
+                                for (;;) {
+                                    asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+                                    if ((uint32_t)(v >> 32) == expect) break;
+                                    if (*abort_flag != 0 || clock64() - t0 > 2000000000ll) { ok = false; break; }
+                                }
+                                uint32_t d = (uint32_t)v;
+                                if (2 * i + 1 >= xcols) d &= 0xFFFFu;             // odd K: the column beyond it stays zero
+                                sts32(xb + SG_A_BYTES + m * SG_XPITCH + i * 4, d);
+                            }
+                        if (!__all_sync(0xffffffffu, ok)) atomicExch(&g_stream_status, 207);
+                    }
+                    if (!__all_sync(0xffffffffu, ok)) { *abort_flag = 1; break; }
+                    __syncwarp();                                                // the staging buffer is free again
+                    if (more) request_x();                                       // the next stage of this warp
+                    if (lane == 0) mbar_arrive(xfull_bar(my_x));
+                } else if (my_L->x_bulk_ok) {
                     // x: one bulk copy per batch row, tracked by the slot's barrier (columns beyond K keep their zeros)
                     __syncwarp();
                     if (lane == 0) {
@@ -1214,23 +1330,26 @@ extern "C" int mpsbnb_gemv_4bit_group_run(const mpsbnb_group_plan *plan, void *s
     args.lins = reinterpret_cast<const StreamLinear *>(plan->dev);
     args.units = reinterpret_cast<const StreamUnit *>(reinterpret_cast<const unsigned char *>(plan->dev) + plan->units_offset);
     args.nunits = plan->n_units; args.M = plan->M; args.quant_type = plan->quant_type;
-    if (plan->wait_n > 0) {
-        if (plan->wait_flags == nullptr || plan->wait_step == nullptr || plan->wait_n > 32) return MPSBNB_ERR_INVALID_ARG;
+    const bool tagged = plan->ep.acc != nullptr && plan->ep.count_tiles == 2;   // x and h travel in tagged form: no flags
+    if (plan->wait_n > 0 || tagged) {
+        if (plan->wait_step == nullptr || plan->wait_n > 32 || (plan->wait_n > 0 && plan->wait_flags == nullptr)) return MPSBNB_ERR_INVALID_ARG;
         args.wait_flags = plan->wait_flags; args.wait_step = plan->wait_step;
-        args.wait_n = plan->wait_n; args.wait_mul = plan->wait_mul; args.wait_add = plan->wait_add;
+        args.wait_n = tagged ? 0 : plan->wait_n; args.wait_mul = plan->wait_mul; args.wait_add = plan->wait_add;
         args.wait_seg_mul = plan->wait_seg_mul > 0 ? plan->wait_seg_mul : 1;
     }
     if (plan->ep.acc != nullptr) {
         const mpsbnb_group_epilogue &e = plan->ep;
         if (e.peer_h == nullptr || e.counter == nullptr || e.M != plan->M || e.hs <= 0 || e.hs % 8 != 0 || e.nranks <= 0 ||
-            e.nranks > 32 || e.rank < 0 || e.rank >= e.nranks || e.H < e.hs * e.nranks || (e.peer_flags != nullptr && e.step == nullptr) ||
+            e.nranks > 32 || e.rank < 0 || e.rank >= e.nranks || e.H < e.hs * e.nranks || ((e.peer_flags != nullptr || tagged) && e.step == nullptr) ||
+            (tagged && (e.tile_cnt == nullptr || e.H % 2 != 0)) ||
             (e.tile_cnt != nullptr && (e.tile_expect <= 0 || e.tile_expect != plan->acc_parts)))
             return MPSBNB_ERR_INVALID_ARG;
         args.ep = e;
+        args.x_ll = e.count_tiles == 2 ? 1 : 0;
     }
     const bool coop = plan->n_segments > 1;
-    if (coop && (plan->ep.tile_cnt == nullptr || plan->wait_n <= 0 || plan->ep.peer_flags == nullptr))
-        return MPSBNB_ERR_INVALID_ARG;                             // later segments need the streamed closing step and its flags
+    if (coop && (plan->ep.tile_cnt == nullptr || (!tagged && (plan->wait_n <= 0 || plan->ep.peer_flags == nullptr))))
+        return MPSBNB_ERR_INVALID_ARG;                             // later segments need the streamed closing step and its flags or tags
     const bool pdl = (plan->flags & MPSBNB_GROUP_PDL) != 0 && !coop;
     return plan->x_dtype == MPSBNB_F16 ? launch_stream<__half>(args, (cudaStream_t)stream, pdl, coop)
                                        : launch_stream<__nv_bfloat16>(args, (cudaStream_t)stream, pdl, coop);

@@ -95,13 +95,17 @@ class LayerStack:
 
     def __init__(self, cfg: StackConfig, device, quant_type: str = "nf4", double_quant: bool = True,
                  layers: Optional[int] = None, rank: int = 0, world: int = 1, seed: int = 1000,
-                 dtype: torch.dtype = torch.float16, group=None, use_pdl: bool = True, fused_exchange: bool = True, boundary: Optional[str] = None, persistent: bool = True, mid_batch_tcgen05: bool = True, emulate_peers: bool = False):
+                 dtype: torch.dtype = torch.float16, group=None, use_pdl: bool = True, fused_exchange: bool = True, boundary: Optional[str] = None, persistent: bool = True, mid_batch_tcgen05: bool = True, emulate_peers: bool = False,
+                 tagged_exchange: Optional[bool] = None):
         self.cfg, self.device, self.dtype = cfg, torch.device(device), dtype
         self.layers = cfg.layers if layers is None else layers
         self.rank, self.world, self.group = rank, world, group
         # timing aid: run ONE rank's shard of a `world`-way split on this GPU alone, every peer pointer aimed at this
         # GPU's own buffers (the per-GPU work of the sharded stack without NVLink; the result is not the model's)
         self.emulate_peers = emulate_peers and world > 1
+        # one-launch step across GPUs: h travels as {values, tag} entries (no flag or fence on the layer boundary's path);
+        # None = where it pays (batch 1, more than one GPU)
+        self.tagged_exchange = tagged_exchange
         # programmatic dependent launch between the per-layer kernels (single GPU: no NCCL kernel in between)
         self.use_pdl = use_pdl and world == 1
         # world > 1, batch <= 8: the layer boundary stores its shard of h into every rank's buffer over NVLink and
@@ -190,10 +194,19 @@ class LayerStack:
         cfg, dev, g, lib = self.cfg, self.device, self.world, N.lib()
         self._close_exchange()
         esz = torch.empty(0, dtype=self.dtype).element_size()
+        # the one-launch-per-step form exchanges h in TAGGED form: 8-byte entries {two values, tag} (twice the bytes; no
+        # flags or fences on the way, see mpsbnb_tagged_write in the header)
+        self._tagged = self._persist and cfg.hidden % 2 == 0 and (
+            (M == 1 and self.world > 1) if self.tagged_exchange is None else bool(self.tagged_exchange))
+        if self._tagged:
+            esz *= 2
         nb = self._nbuf
         h_bytes = (nb * M * cfg.hidden * esz + 255) // 256 * 256
         self._xbuf = torch.zeros(h_bytes + 512, dtype=torch.uint8, device=dev)
-        self.hbuf = self._xbuf[:nb * M * cfg.hidden * esz].view(self.dtype).view(nb, M, cfg.hidden)
+        if self._tagged:
+            self.hbuf = self._xbuf[:nb * M * cfg.hidden * esz].view(torch.int64).view(nb, M, cfg.hidden // 2)
+        else:
+            self.hbuf = self._xbuf[:nb * M * cfg.hidden * esz].view(self.dtype).view(nb, M, cfg.hidden)
         self.flags = self._xbuf[h_bytes:h_bytes + 4 * g].view(torch.int32)
         self.acks = self._xbuf[h_bytes + 256:h_bytes + 256 + 4 * g].view(torch.int32)
         self.step_ctr = torch.zeros(1, dtype=torch.int32, device=dev)
@@ -202,7 +215,11 @@ class LayerStack:
         if self.emulate_peers:
             base = self._xbuf.data_ptr()
             one = M * cfg.hidden * esz
-            self._peer_h = [torch.tensor([base + p * one] * g, dtype=torch.int64, device=dev) for p in range(nb)]
+            # tagged form: no flags to fake, so "peer" r's copy of this rank's columns is aimed at rank r's columns of the
+            # same buffer - every column then receives a (meaningless but correctly tagged) value, as on g real GPUs
+            shift = (cfg.hidden // g) * esz if self._tagged else 0
+            self._peer_h = [torch.tensor([base + p * one + (r - self.rank) * shift for r in range(g)], dtype=torch.int64, device=dev)
+                            for p in range(nb)]
             # the kernels write flag pointer[r] + own rank: aim pointer r at flags[r - rank] so that slot r is raised
             self._peer_flags = torch.tensor([base + h_bytes + 4 * (r - self.rank) for r in range(g)], dtype=torch.int64, device=dev)
             self._peer_acks = torch.tensor([base + h_bytes + 256 + 4 * (r - self.rank) for r in range(g)], dtype=torch.int64, device=dev)
@@ -342,10 +359,17 @@ class LayerStack:
         ep.tile_cnt, ep.tile_expect = self._tile_cnt.data_ptr(), plan.acc_parts
         # flags[r] counts the 32-row tiles of h that rank r has closed and stored here since the start (every closed
         # tile adds 1 on every rank): the input of layer l of step s is complete when every count is (s L + l) T
-        T = self._tiles_per_shard = (cfg.hidden // g + 31) // 32
-        ep.count_tiles = 1
-        plan.wait_flags, plan.wait_step = self.flags.data_ptr(), self.step_ctr.data_ptr()
-        plan.wait_n, plan.wait_mul, plan.wait_add, plan.wait_seg_mul = g, L * T, 0, T
+        if self._tagged:
+            # tagged exchange: the input of layer l of step s carries the tag s (L + 1) + l; nothing else is waited for
+            ep.count_tiles, ep.mul, ep.add = 2, L + 1, 1
+            plan.wait_flags, plan.wait_step = None, self.step_ctr.data_ptr()
+            plan.wait_n, plan.wait_mul, plan.wait_add, plan.wait_seg_mul = 0, L + 1, 0, 1
+        else:
+            # flags[r] counts the 32-row tiles of h that rank r has closed and stored here since the start
+            T = self._tiles_per_shard = (cfg.hidden // g + 31) // 32
+            ep.count_tiles = 1
+            plan.wait_flags, plan.wait_step = self.flags.data_ptr(), self.step_ctr.data_ptr()
+            plan.wait_n, plan.wait_mul, plan.wait_add, plan.wait_seg_mul = g, L * T, 0, T
         self._plans = [plan]
 
     def _gemv(self, pr: _Proj, x: torch.Tensor, y: torch.Tensor, M: int):
@@ -370,11 +394,15 @@ class LayerStack:
                 N.check(lib.mpsbnb_flags_wait(N.ptr(self.acks), C.c_int(g), N.ptr(self.step_ctr), C.c_int(1), C.c_int(0),
                                               C.c_int(0), N.stream()), "flags_wait")
             N.check(lib.mpsbnb_gemv_4bit_group_run(C.byref(self._plans[0]), N.stream()), "gemv_4bit_group_run")
-            if g > 1:     # ... and every rank's last shard has landed here
-                T = self._tiles_per_shard
-                N.check(lib.mpsbnb_flags_wait(N.ptr(self.flags), C.c_int(g), N.ptr(self.step_ctr), C.c_int(L * T), C.c_int(L * T),
-                                              C.c_int(0), N.stream()), "flags_wait")
-            self.h_out.copy_(self.hbuf[L % self._nbuf])
+            if self._tagged:   # the result is complete when every entry carries the tag of "layer L"
+                N.check(lib.mpsbnb_tagged_read(N.ptr(self.hbuf[L % self._nbuf]), N.i64(M), N.i64(cfg.hidden), N.ptr(self.h_out),
+                                               N.ptr(self.step_ctr), C.c_int(L + 1), C.c_int(L), N.stream()), "tagged_read")
+            else:
+                if g > 1:     # ... and every rank's last shard has landed here
+                    T = self._tiles_per_shard
+                    N.check(lib.mpsbnb_flags_wait(N.ptr(self.flags), C.c_int(g), N.ptr(self.step_ctr), C.c_int(L * T), C.c_int(L * T),
+                                                  C.c_int(0), N.stream()), "flags_wait")
+                self.h_out.copy_(self.hbuf[L % self._nbuf])
             N.check(lib.mpsbnb_counter_add(N.ptr(self.step_ctr), C.c_int(1), N.stream()), "counter_add")
             if g > 1:
                 N.check(lib.mpsbnb_flags_push(N.ptr(self._peer_acks), C.c_int(self.rank), C.c_int(g), N.ptr(self.step_ctr),
@@ -462,6 +490,10 @@ class LayerStack:
     def _load_input(self):
         """h = x_in, e = tile(x_in): the stack's input stage (uses the expand kernel with one rank)."""
         cfg = self.cfg
+        if self._persist and getattr(self, "_tagged", False):
+            N.check(N.lib().mpsbnb_tagged_write(N.ptr(self.x_in), N.i64(self._M), N.i64(cfg.hidden), N.ptr(self.hbuf[0]),
+                                                N.ptr(self.step_ctr), C.c_int(self.layers + 1), C.c_int(0), N.stream()), "tagged_write")
+            return
         N.check(N.lib().mpsbnb_stack_expand(N.ptr(self.x_in), N.dt(self.dtype), N.i64(1), N.i64(self._M),
                                             N.i64(cfg.hidden), N.i64(cfg.ffn), N.ptr(self._x_of_layer(0)), N.ptr(self.e),
                                             N.stream()), "stack_expand")

@@ -87,6 +87,28 @@ def test_whole_stack_in_one_launch(M, qt, dq):
     assert_device_ok()
 
 
+@pytest.mark.parametrize("M,hidden,ffn", [(1, 256, 704), (3, 256, 704), (1, 2048, 5120), (1, 1024, 2816), (2, 2048, 5120)])
+def test_whole_stack_in_one_launch_tagged_exchange(M, hidden, ffn):
+    """tagged_exchange=True: h travels between layers as {two values, tag} entries, no flags.  Batch 1 with stages of whole
+    runs of four columns goes through the loaders' staging buffers; everything else reads the entries where they lie
+    (704 = a short last stage that straddles the period of `down`; 2816 = 2 x 1024 + 768; batch 2 and 3)."""
+    cfg = S.StackConfig("tiny", hidden=hidden, ffn=ffn, kv=64, layers=4)
+    st = S.LayerStack(cfg, device="cuda:0", seed=12, boundary="stream", persistent=True, tagged_exchange=True)
+    x = np.random.default_rng(20 + M).standard_normal((M, cfg.hidden)).astype(np.float16)
+    for use_graph in (False, True):
+        st.prepare(M, use_graph=use_graph)
+        assert st._tagged
+        ref_h, ref_out = oracle_stack(st, x)
+        for _ in range(3):
+            h = st.step(torch.from_numpy(x).cuda())
+            torch.cuda.synchronize()
+            assert st.check_status() == 0
+            assert rel_err(to_np(h), ref_h) <= 1e-2, use_graph
+            for name in ("q", "k", "v", "gate", "up"):
+                assert rel_err(to_np(st.out[name]), ref_out[name]) <= 1e-2, name
+    assert_device_ok()
+
+
 def test_llama7b_layer_shapes_one_layer():
     """One layer at the real Llama-2-7B widths, batch 1 (the benchmark's unit of work)."""
     st = S.LayerStack(S.LLAMA2_7B, device="cuda:0", layers=1, seed=9)
