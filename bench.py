@@ -329,12 +329,16 @@ def oracle_stack_rows(ref_stack, x_rows):
     return h
 
 
+TAGGED = {"auto": None, "tagged": True, "flags": False}
+
+
 def stack_parity(S, torch, dist, cfg, M, rank, world, local, args, layers=2, sample=4):
     """Reduced-depth instance of the benchmarked stack (same widths, same sharding, same kernels and exchange) run
     once and compared with the C oracle on `sample` rows of the batch.  Returns the parity figure on every rank."""
     import numpy as np
     st = S.LayerStack(cfg, device=f"cuda:{local}", rank=rank, world=world, layers=layers,
-                      fused_exchange=args.exchange == "fused", boundary=args.boundary, persistent=not args.per_layer)
+                      fused_exchange=args.exchange == "fused", boundary=args.boundary, persistent=not args.per_layer,
+                      tagged_exchange=TAGGED[args.handoff])
     st.prepare(M, use_graph=True)
     gen = torch.Generator(device="cpu"); gen.manual_seed(7)
     x = torch.randn(M, cfg.hidden, generator=gen).half()
@@ -445,7 +449,8 @@ def run_gpu(args, cfg):
     peaks = load_peaks()
     M = args.batch
     stack = S.LayerStack(cfg, device=f"cuda:{local}", rank=rank, world=world, layers=args.layers,
-                         fused_exchange=args.exchange == "fused", boundary=args.boundary, persistent=not args.per_layer)
+                         fused_exchange=args.exchange == "fused", boundary=args.boundary, persistent=not args.per_layer,
+                         tagged_exchange=TAGGED[args.handoff])
 
     def barrier():
         if world > 1:
@@ -558,6 +563,9 @@ def main():
     ap.add_argument("--int8-only", action="store_true", help="only the INT8 / FP8 / outlier-split object (BASELINE config 4)")
     ap.add_argument("--exchange", default="fused", choices=["fused", "nccl"],
                     help="N > 1: layer boundary by peer stores + flags (default) or by an NCCL all-gather")
+    ap.add_argument("--handoff", default="auto", choices=["auto", "tagged", "flags"],
+                    help="N > 1, one launch per step: how a layer learns that its input is complete - tagged {values, tag} "
+                         "entries, or per-rank counts of closed tiles (auto: tagged at batch 1)")
     ap.add_argument("--boundary", default=None, choices=["kernel", "inline", "stream"],
                     help="layer boundary: its own small kernel, the closing step of the GEMV launch, or streamed tile "
                          "by tile from inside the launch (default)")

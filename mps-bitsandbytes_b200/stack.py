@@ -171,8 +171,12 @@ class LayerStack:
         self._plans = None
         self._fused = self.fused_exchange and M <= 8
         self._stream = self.boundary == "stream" and M <= 8 and (g == 1 or self._fused)
-        self._nbuf = 3 if self._stream else 2
         self._persist = self.persistent and self._stream
+        # h buffers a step rotates over.  One launch per step: one per layer plus the result.  Nothing in THIS stack waits
+        # for a CTA's q / k / v / gate / up units (down reads h, not gate * up), so such a CTA may fall layers behind the
+        # o / down chain; with a buffer per layer none is rewritten while a late reader still wants it, and the step's end
+        # (the kernel's end; across GPUs the acknowledgement counts) separates the steps.
+        self._nbuf = (self.layers + 1) if self._persist else (3 if self._stream else 2)
         self._inline = self.in_kernel_boundary and M <= 8         # closing step inside the GEMV launch (default kernel only)
         if self._fused or self._persist:
             self._setup_exchange(M)

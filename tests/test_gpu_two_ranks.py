@@ -11,7 +11,7 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def _worker(rank, world, port, M, fused, boundary, persistent):
+def _worker(rank, world, port, M, fused, boundary, persistent, tagged=None):
     import torch.distributed as dist
     from mps_bitsandbytes_b200 import stack as S
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
@@ -22,7 +22,8 @@ def _worker(rank, world, port, M, fused, boundary, persistent):
     whole = S.LayerStack(cfg, device=f"cuda:{rank}", seed=21)                   # the same model on every rank
     whole.prepare(M, use_graph=False)
     ref = whole.step(x).float().clone()
-    part = S.LayerStack(cfg, device=f"cuda:{rank}", seed=21, rank=rank, world=world, fused_exchange=fused, boundary=boundary, persistent=persistent)
+    part = S.LayerStack(cfg, device=f"cuda:{rank}", seed=21, rank=rank, world=world, fused_exchange=fused, boundary=boundary, persistent=persistent,
+                        tagged_exchange=tagged)
     ok = True
     for use_graph in (False, True):
         part.prepare(M, use_graph=use_graph)
@@ -43,19 +44,21 @@ def _worker(rank, world, port, M, fused, boundary, persistent):
     os._exit(0 if int(flag.item()) == 1 else 1)
 
 
-@pytest.mark.parametrize("M,fused,boundary,persistent", [(1, True, "kernel", False), (4, True, "inline", False),
-                                                         (1, True, "stream", False), (8, True, "stream", False),
-                                                         (1, True, "stream", True), (5, True, "stream", True),
-                                                         (1, False, "kernel", False), (16, True, "kernel", False)])
-def test_two_rank_stack_matches_single_gpu(M, fused, boundary, persistent):
-    """fused: peer stores + flags at the layer boundary (batch <= 8); otherwise NCCL all-gather."""
+@pytest.mark.parametrize("M,fused,boundary,persistent,tagged", [
+    (1, True, "kernel", False, None), (4, True, "inline", False, None), (1, True, "stream", False, None),
+    (8, True, "stream", False, None), (1, True, "stream", True, None), (5, True, "stream", True, None),
+    (1, True, "stream", True, False), (2, True, "stream", True, True),
+    (1, False, "kernel", False, None), (16, True, "kernel", False, None)])
+def test_two_rank_stack_matches_single_gpu(M, fused, boundary, persistent, tagged):
+    """fused: peer stores at the layer boundary (batch <= 8) - with flags, or (one launch per step, batch 1 unless forced)
+    as tagged entries; otherwise NCCL all-gather."""
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     import torch.multiprocessing as mp
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
         port = s.getsockname()[1]
-    ctx = mp.spawn(_worker, args=(2, port, M, fused, boundary, persistent), nprocs=2, join=False)
+    ctx = mp.spawn(_worker, args=(2, port, M, fused, boundary, persistent, tagged), nprocs=2, join=False)
     # bounded: a rank that never joins must not hold the suite
     for p in ctx.processes:
         p.join(timeout=180)
