@@ -565,7 +565,7 @@ def main():
                     help="N > 1: layer boundary by peer stores + flags (default) or by an NCCL all-gather")
     ap.add_argument("--handoff", default="auto", choices=["auto", "tagged", "flags"],
                     help="N > 1, one launch per step: how a layer learns that its input is complete - tagged {values, tag} "
-                         "entries, or per-rank counts of closed tiles (auto: tagged at batch 1)")
+                         "entries, or per-rank counts of closed tiles (auto: counts)")
     ap.add_argument("--boundary", default=None, choices=["kernel", "inline", "stream"],
                     help="layer boundary: its own small kernel, the closing step of the GEMV launch, or streamed tile "
                          "by tile from inside the launch (default)")

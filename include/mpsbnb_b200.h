@@ -174,7 +174,10 @@ typedef struct mpsbnb_group_epilogue {
                                * no second fence: waiters then expect a multiple of the tiles per shard, see wait_seg_mul);
                                * 2 = no flags at all: peer_h are TAGGED buffers (8-byte entries {two values, tag}, tag =
                                * step * mul + add + segment) and every linear of the plan reads its x in that form, expecting
-                               * the tag (*wait_step) * wait_mul + wait_add + segment * wait_seg_mul */
+                               * the tag (*wait_step) * wait_mul + wait_add + segment * wait_seg_mul.  A linear then starts as
+                               * soon as ITS columns carry the tag, so segments overlap: acc holds TWO accumulators
+                               * [2][M][hs] and tile_cnt two sets of counts [2][ceil(hs / 32)], indexed by segment parity,
+                               * and the accumulating linears of segment s point their acc at copy s & 1 */
 } mpsbnb_group_epilogue;
 
 typedef struct mpsbnb_group_plan {

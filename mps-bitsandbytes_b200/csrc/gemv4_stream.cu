@@ -60,6 +60,8 @@ constexpr int SG_MAX_M = 8;
 // status word of this translation unit (device code is not linked relocatably); read by
 // stream_status_fetch() on behalf of mpsbnb_device_status()
 static __device__ int g_stream_status = 0;
+// the FIRST wait that gave up names the cause; the others give up because of it
+__device__ __forceinline__ void sg_fail(int code) { atomicCAS(&g_stream_status, 0, code); }
 
 #ifdef MPSBNB_TRACE
 // Development aid (compiled in with -DMPSBNB_TRACE only): per segment, when CTA 0's first loader began and ended its
@@ -69,10 +71,13 @@ __device__ __forceinline__ unsigned long long trace_now() { unsigned long long t
 #define MPSBNB_TRACE_SET(slot, seg) do { if ((seg) >= 0 && (seg) < 256) g_trace[(slot) * 256 + (seg)] = trace_now(); } while (0)
 // cycles CTA 0's roles spend inside each kind of barrier wait (lane 0 of every warp adds its own), [15] = CTA 0's total
 static __device__ unsigned long long g_wait[16];
+static __device__ unsigned int g_fail[8];
+#define SG_FAIL_DETAIL(a_, b_, c_, d_, e_) do { if (atomicCAS(&g_fail[0], 0u, 1u) == 0u) { g_fail[1] = blockIdx.x; g_fail[2] = (a_); g_fail[3] = (b_); g_fail[4] = (c_); g_fail[5] = (d_); g_fail[6] = (e_); } } while (0)
 #define SG_TIMED(idx, expr) ([&]() { const long long t0_ = clock64(); const bool r_ = (expr); if (blockIdx.x == 0 && (threadIdx.x & 31) == 0) atomicAdd(&g_wait[idx], (unsigned long long)(clock64() - t0_)); return r_; }())
 #else
 #define MPSBNB_TRACE_SET(slot, seg) do { } while (0)
 #define SG_TIMED(idx, expr) (expr)
+#define SG_FAIL_DETAIL(a_, b_, c_, d_, e_) do { } while (0)
 #endif
 
 
@@ -454,7 +459,7 @@ __global__ void __launch_bounds__(SG_THREADS, 1) mpsbnb_decode4_stream_kernel(co
                 const bool m3 = L->map3d != 0;
                 bool ok = true;
                 for (int s = un.s_begin; s < un.s_end; ++s) {
-                    if (!SG_TIMED(0, mbar_wait_sleep(empty_bar(slot), ph ^ 1u, abort_flag, a.sleep_other))) { atomicExch(&g_stream_status, 201); *abort_flag = 1; ok = false; break; }
+                    if (!SG_TIMED(0, mbar_wait_sleep(empty_bar(slot), ph ^ 1u, abort_flag, a.sleep_other))) { sg_fail(201); *abort_flag = 1; ok = false; break; }
                     const uint32_t bar = full_bar(slot), dst = sm.addr(slot);
                     mbar_arrive_expect_tx(bar, SG_W_BYTES);
                     if (m3) {
@@ -482,7 +487,7 @@ __global__ void __launch_bounds__(SG_THREADS, 1) mpsbnb_decode4_stream_kernel(co
         // and re-arms the accumulator - the round trip of the count never holds this warp up
         int mail_i = 0; uint32_t mail_ph = 0;
         auto post = [&](int tile) {
-            if (!mbar_wait_sleep(mail_empty(mail_i), mail_ph ^ 1u, abort_flag, a.sleep_other)) { atomicExch(&g_stream_status, 208); *abort_flag = 1; return; }
+            if (!mbar_wait_sleep(mail_empty(mail_i), mail_ph ^ 1u, abort_flag, a.sleep_other)) { sg_fail(208); *abort_flag = 1; return; }
             if (lane == 0) { sts32(s_mail + 4u * mail_i, (uint32_t)tile); mbar_arrive(mail_full(mail_i)); }
             __syncwarp();
             if (++mail_i == SG_MAIL) { mail_i = 0; mail_ph ^= 1u; }
@@ -497,7 +502,7 @@ __global__ void __launch_bounds__(SG_THREADS, 1) mpsbnb_decode4_stream_kernel(co
             float *Lacc = L->acc;
             void *Ly = L->y;
             const int buf = uc & 1;
-            if (!SG_TIMED(1, mbar_wait_sleep(red_full(buf), (uint32_t)(uc >> 1) & 1u, abort_flag, a.sleep_other))) { atomicExch(&g_stream_status, 204); *abort_flag = 1; break; }
+            if (!SG_TIMED(1, mbar_wait_sleep(red_full(buf), (uint32_t)(uc >> 1) & 1u, abort_flag, a.sleep_other))) { sg_fail(204); *abort_flag = 1; break; }
             const float *red = reinterpret_cast<const float *>(p_generic0 + s_red + buf * SG_RED_BYTES);
             const int n = un.row0 + lane;
             for (int m = 0; m < a.M; ++m) {
@@ -521,7 +526,8 @@ __global__ void __launch_bounds__(SG_THREADS, 1) mpsbnb_decode4_stream_kernel(co
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(red_empty(buf));
-            if (a.ep.tile_cnt != nullptr && Lacc == a.ep.acc && Lacc != nullptr) {
+            if (a.ep.tile_cnt != nullptr && Lacc != nullptr &&
+                (Lacc == a.ep.acc || (a.ep.count_tiles == 2 && Lacc == a.ep.acc + (int64_t)a.M * a.ep.hs))) {   // (tagged: two copies)
                 // streamed closing step: the closer warp counts this unit's contribution to its 32-row tile.  The mailbox
                 // barrier (release / acquire inside the CTA) orders this warp's accumulator updates before the closer's
                 // count, which is a release and an acquire at GPU scope.
@@ -538,7 +544,7 @@ __global__ void __launch_bounds__(SG_THREADS, 1) mpsbnb_decode4_stream_kernel(co
             const int nbuf = a.ep.nbuf > 1 ? a.ep.nbuf : 1;
             int mi = 0; uint32_t mph = 0;
             while (!*abort_flag) {
-                if (!SG_TIMED(11, mbar_wait_sleep(mail_full(mi), mph, abort_flag, a.sleep_other))) { atomicExch(&g_stream_status, 209); *abort_flag = 1; break; }
+                if (!SG_TIMED(11, mbar_wait_sleep(mail_full(mi), mph, abort_flag, a.sleep_other))) { sg_fail(209); *abort_flag = 1; break; }
 #ifdef MPSBNB_TRACE
                 const long long tclose0 = clock64();
 #endif
@@ -551,8 +557,12 @@ __global__ void __launch_bounds__(SG_THREADS, 1) mpsbnb_decode4_stream_kernel(co
                 {
                     int old = 0;
                     // counts 0 .. expect - 1 and wraps to 0 by itself: the count needs no re-arming store
+                    // Tagged exchange: a unit of the next segment runs as soon as ITS columns of x carry the tag, possibly before
+                    // this tile of this segment is closed - counts and accumulators exist twice, by segment parity (a tile
+                    // of segment s + 1 cannot close before every tile of segment s has: two copies are enough).
+                    const int par_cnt = a.ep.count_tiles == 2 ? (seg & 1) * ((a.ep.hs + SG_ROWS - 1) / SG_ROWS) : 0;
                     if (lane == 0)
-                        asm volatile("atom.inc.acq_rel.gpu.global.u32 %0, [%1], %2;" : "=r"(old) : "l"(a.ep.tile_cnt + tile), "r"(a.ep.tile_expect - 1) : "memory");
+                        asm volatile("atom.inc.acq_rel.gpu.global.u32 %0, [%1], %2;" : "=r"(old) : "l"(a.ep.tile_cnt + par_cnt + tile), "r"(a.ep.tile_expect - 1) : "memory");
                     old = __shfl_sync(0xffffffffu, old, 0);
                     if (old != a.ep.tile_expect - 1) continue;       // not the tile's last contribution
                 }
@@ -567,7 +577,7 @@ __global__ void __launch_bounds__(SG_THREADS, 1) mpsbnb_decode4_stream_kernel(co
                     const int c = tile * SG_ROWS + lane;
                     for (int m = 0; m < a.M; ++m) {
                         float v = 0.0f;
-                        if (c < a.ep.hs) v = atomicExch(a.ep.acc + (int64_t)m * a.ep.hs + c, 0.0f);
+                        if (c < a.ep.hs) v = atomicExch(a.ep.acc + ((int64_t)(seg & 1) * a.M + m) * a.ep.hs + c, 0.0f);
                         const float vn = __shfl_down_sync(0xffffffffu, v, 1);
                         if ((lane & 1) == 0 && c < a.ep.hs) {
                             const unsigned long long w = ((unsigned long long)tag << 32) | pair_bits<XT>(a.ep.alpha * v, a.ep.alpha * vn);
@@ -723,7 +733,7 @@ __global__ void __launch_bounds__(SG_THREADS, 1) mpsbnb_decode4_stream_kernel(co
                 float nxt[16];
                 more = advance_to_mine();
                 if (more) read_scales(L, un.row0, s, nxt);
-                if (!SG_TIMED(2, mbar_wait_sleep(xempty_bar(my_x), my_ph ^ 1u, abort_flag, a.sleep_other))) { atomicExch(&g_stream_status, 202); *abort_flag = 1; break; }
+                if (!SG_TIMED(2, mbar_wait_sleep(xempty_bar(my_x), my_ph ^ 1u, abort_flag, a.sleep_other))) { sg_fail(202); *abort_flag = 1; break; }
                 const uint32_t xb = s_xs + (uint32_t)my_x * xs_bytes;
                 if (a.wait_n > 0 && my_L->segment > ready_seg) {
                     // x of this segment is written by closing steps: of the previous launch or segment, on this GPU and,
@@ -743,7 +753,7 @@ __global__ void __launch_bounds__(SG_THREADS, 1) mpsbnb_decode4_stream_kernel(co
                     }
                     arrived = __all_sync(0xffffffffu, arrived);
                     asm volatile("fence.proxy.async;" ::: "memory");      // x is then read by bulk copies (async proxy)
-                    if (!arrived) { atomicExch(&g_stream_status, 207); *abort_flag = 1; break; }
+                    if (!arrived) { sg_fail(207); *abort_flag = 1; break; }
                     if (blockIdx.x == 0 && me == 0 && lane == 0) MPSBNB_TRACE_SET(1, my_L->segment);
                     ready_seg = my_L->segment;
                 }
@@ -764,11 +774,16 @@ __global__ void __launch_bounds__(SG_THREADS, 1) mpsbnb_decode4_stream_kernel(co
                         // examined (a loader's stages lie SG_LOADERS apart: the round trip to L2 is long over)
                         const uint32_t sb = s_stage + (uint32_t)me * 4096u;
                         const int npairs = xcols >> 1;
+                        const unsigned long long *src = x2 + (((my_s * (SG_STAGE_BLOCKS * 64)) % my_L->x_period) >> 1);
+                        if (!SG_TIMED(13, mbar_wait_sleep(sfull_bar(me), sph, abort_flag, a.sleep_other))) { sg_fail(210); ok = false; }
+                        sph ^= 1u;
                         long long t0 = 0;
-                        for (;;) {
-                            if (!SG_TIMED(13, mbar_wait_sleep(sfull_bar(me), sph, abort_flag, a.sleep_other))) { atomicExch(&g_stream_status, 210); ok = false; break; }
-                            sph ^= 1u;
+                        // First pass: the staged copy.  If an entry there is late, the following passes read the entries where
+                        // they lie with system-scope loads - NOT another bulk copy: a bulk copy is a weak read, and one that races
+                        // with another GPU's store was seen to keep returning the old entry for good.
+                        for (bool staged = true; ok; staged = false) {
                             bool good = true;
+                            uint32_t bad_tag = 0u; int bad_c = -1;               // (trace builds report the first entry that is late)
                             // 16-byte chunks (two entries) c = lane + 32 j; four loads are issued before the first value is looked at
 #pragma unroll
                             for (int h = 0; h < 2; ++h) {
@@ -776,26 +791,29 @@ __global__ void __launch_bounds__(SG_THREADS, 1) mpsbnb_decode4_stream_kernel(co
 #pragma unroll
                                 for (int j = 0; j < 4; ++j) {
                                     const int c = lane + 32 * (4 * h + j);
-                                    if (2 * c < npairs)
+                                    if (2 * c >= npairs) { r[j][1] = expect; r[j][3] = expect; r[j][0] = 0u; r[j][2] = 0u; }
+                                    else if (staged)
                                         asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(r[j][0]), "=r"(r[j][1]), "=r"(r[j][2]), "=r"(r[j][3]) : "r"(sb + (uint32_t)c * 16u));
-                                    else { r[j][1] = expect; r[j][3] = expect; r[j][0] = 0u; r[j][2] = 0u; }
+                                    else {
+                                        asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(r[j][0]), "=r"(r[j][1]) : "l"(src + 2 * c) : "memory");
+                                        asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(r[j][2]), "=r"(r[j][3]) : "l"(src + 2 * c + 1) : "memory");
+                                    }
                                 }
 #pragma unroll
                                 for (int j = 0; j < 4; ++j) {
                                     const int c = lane + 32 * (4 * h + j);
                                     good = good && r[j][1] == expect && r[j][3] == expect;
+                                    if (bad_c < 0 && (r[j][1] != expect || r[j][3] != expect)) { bad_c = c; bad_tag = r[j][1] != expect ? r[j][1] : r[j][3]; }
                                     if (2 * c < npairs)                           // K is a multiple of 4 here: no column beyond it
                                         asm volatile("st.shared.v2.u32 [%0], {%1, %2};" :: "r"(xb + (uint32_t)SG_A_BYTES + (uint32_t)c * 8u), "r"(r[j][0]), "r"(r[j][2]) : "memory");
                                 }
                             }
                             if (__all_sync(0xffffffffu, good)) break;
                             if (t0 == 0) t0 = clock64();
-                            if (*abort_flag != 0 || clock64() - t0 > 2000000000ll) { atomicExch(&g_stream_status, 207); ok = false; break; }
-                            if (lane == 0) {                                      // some entry is not there yet: fetch the row again
-                                mbar_arrive_expect_tx(sfull_bar(me), (uint32_t)npairs * 8u);
-                                bulk_load_1d(sb, x2 + (((my_s * (SG_STAGE_BLOCKS * 64)) % my_L->x_period) >> 1), (uint32_t)npairs * 8u, sfull_bar(me));
+                            if (*abort_flag != 0 || clock64() - t0 > 2000000000ll) {
+                                if (*abort_flag == 0 && bad_c >= 0) SG_FAIL_DETAIL(expect, bad_tag, (uint32_t)((my_L->segment << 16) | my_s), (uint32_t)bad_c, (uint32_t)*a.wait_step);
+                                sg_fail(207); ok = false;
                             }
-                            __syncwarp();
                         }
                     } else {
                         // a batch above 1, a stage that straddles the period, an odd offset: the entries are read where they lie
@@ -814,7 +832,7 @@ __global__ void __launch_bounds__(SG_THREADS, 1) mpsbnb_decode4_stream_kernel(co
                                 if (2 * i + 1 >= xcols) d &= 0xFFFFu;             // odd K: the column beyond it stays zero
                                 sts32(xb + SG_A_BYTES + m * SG_XPITCH + i * 4, d);
                             }
-                        if (!__all_sync(0xffffffffu, ok)) atomicExch(&g_stream_status, 207);
+                        if (!__all_sync(0xffffffffu, ok)) sg_fail(207);
                     }
                     if (!__all_sync(0xffffffffu, ok)) { *abort_flag = 1; break; }
                     __syncwarp();                                                // the staging buffer is free again
@@ -921,8 +939,8 @@ __global__ void __launch_bounds__(SG_THREADS, 1) mpsbnb_decode4_stream_kernel(co
 #pragma unroll 1
                 for (; nextq < qe; nextq += SG_GROUPS) {
                     const int s = un.s_begin + (nextq - qb);
-                    if (!SG_TIMED(warp == 0 ? 3 : 6, mbar_wait_sleep(full_bar(slot), ph, abort_flag, a.sleep_cons))) { atomicExch(&g_stream_status, 203); *abort_flag = 1; ok = false; break; }
-                    if (!SG_TIMED(warp == 0 ? 4 : 7, mbar_wait_sleep(xfull_bar(xslot), xph, abort_flag, a.sleep_cons))) { atomicExch(&g_stream_status, 206); *abort_flag = 1; ok = false; break; }
+                    if (!SG_TIMED(warp == 0 ? 3 : 6, mbar_wait_sleep(full_bar(slot), ph, abort_flag, a.sleep_cons))) { sg_fail(203); *abort_flag = 1; ok = false; break; }
+                    if (!SG_TIMED(warp == 0 ? 4 : 7, mbar_wait_sleep(xfull_bar(xslot), xph, abort_flag, a.sleep_cons))) { sg_fail(206); *abort_flag = 1; ok = false; break; }
                     const uint32_t dep = stage_fn(s, nbv, sm.addr(slot), s_xs + (uint32_t)xslot * xs_bytes, empty_bar(slot));
                     __syncwarp();
                     if (lane == 0) mbar_arrive(xempty_bar(xslot) + (dep & a.zero));
@@ -933,7 +951,7 @@ __global__ void __launch_bounds__(SG_THREADS, 1) mpsbnb_decode4_stream_kernel(co
                 // hand the partial sums to the reducer warp (zeros if none of this unit's stages were mine); the
                 // buffer of two units ago must have been drained
                 const int buf = uc & 1;
-                if (!SG_TIMED(warp == 0 ? 5 : 8, mbar_wait_sleep(red_empty(buf), ((uint32_t)(uc >> 1) & 1u) ^ 1u, abort_flag, a.sleep_cons))) { atomicExch(&g_stream_status, 205); *abort_flag = 1; break; }
+                if (!SG_TIMED(warp == 0 ? 5 : 8, mbar_wait_sleep(red_empty(buf), ((uint32_t)(uc >> 1) & 1u) ^ 1u, abort_flag, a.sleep_cons))) { sg_fail(205); *abort_flag = 1; break; }
                 flush_fn(s_red + (uint32_t)(buf * SG_RED_BYTES));
                 __syncwarp();
                 if (lane == 0) mbar_arrive(red_full(buf));
@@ -1163,6 +1181,11 @@ int stream_status_fetch(int *out, bool reset) {
 #ifdef MPSBNB_TRACE
 extern "C" int mpsbnb_debug_trace(unsigned long long *out768) {
     return cudaMemcpyFromSymbol(out768, g_trace, sizeof(unsigned long long) * 768) == cudaSuccess ? 0 : -3;
+}
+extern "C" int mpsbnb_debug_fail(unsigned int *out8) {
+    if (cudaMemcpyFromSymbol(out8, g_fail, sizeof(unsigned int) * 8) != cudaSuccess) return -3;
+    unsigned int z[8] = {0}; cudaMemcpyToSymbol(g_fail, z, sizeof(z));
+    return 0;
 }
 extern "C" int mpsbnb_debug_waits(unsigned long long *out16, int reset) {
     if (cudaMemcpyFromSymbol(out16, g_wait, sizeof(unsigned long long) * 16) != cudaSuccess) return -3;

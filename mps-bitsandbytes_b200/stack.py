@@ -103,8 +103,9 @@ class LayerStack:
         # timing aid: run ONE rank's shard of a `world`-way split on this GPU alone, every peer pointer aimed at this
         # GPU's own buffers (the per-GPU work of the sharded stack without NVLink; the result is not the model's)
         self.emulate_peers = emulate_peers and world > 1
-        # one-launch step across GPUs: h travels as {values, tag} entries (no flag or fence on the layer boundary's path);
-        # None = where it pays (batch 1, more than one GPU)
+        # one-launch step: True = h travels as {values, tag} entries (no flag, fence or acquire on the layer boundary's
+        # path, and a linear starts as soon as ITS columns have arrived; the loaders pay for it by examining tags, 8 % of
+        # a single GPU's streaming rate).  Off unless asked for: per-rank counts of closed tiles are the measured default.
         self.tagged_exchange = tagged_exchange
         # programmatic dependent launch between the per-layer kernels (single GPU: no NCCL kernel in between)
         self.use_pdl = use_pdl and world == 1
@@ -200,8 +201,7 @@ class LayerStack:
         esz = torch.empty(0, dtype=self.dtype).element_size()
         # the one-launch-per-step form exchanges h in TAGGED form: 8-byte entries {two values, tag} (twice the bytes; no
         # flags or fences on the way, see mpsbnb_tagged_write in the header)
-        self._tagged = self._persist and cfg.hidden % 2 == 0 and (
-            (M == 1 and self.world > 1) if self.tagged_exchange is None else bool(self.tagged_exchange))
+        self._tagged = self._persist and cfg.hidden % 2 == 0 and bool(self.tagged_exchange)
         if self._tagged:
             esz *= 2
         nb = self._nbuf
@@ -329,6 +329,8 @@ class LayerStack:
         step * L + l + 1; linears of layer l wait for flags >= step * L + l."""
         cfg, lib, g, L = self.cfg, N.lib(), self.world, self.layers
         n = 7 * L
+        if self._tagged:
+            self.acc2 = torch.zeros(2, M, cfg.hidden // g, dtype=torch.float32, device=self.device)
         descs = (N.Linear4Desc * n)()
         self.out_layers = []
         for l in range(L):
@@ -342,7 +344,7 @@ class LayerStack:
                 d.absmax2 = None if pr.absmax2 is None else pr.absmax2.data_ptr()
                 d.bias = None
                 if pr.name in ("o", "down"):
-                    d.y, d.acc = None, self.acc.data_ptr()
+                    d.y, d.acc = None, (self.acc2[l & 1] if self._tagged else self.acc).data_ptr()
                 else:
                     d.y, d.acc = outs[pr.name].data_ptr(), None
                 d.N, d.K, d.segment = pr.n, pr.k, l
@@ -354,9 +356,10 @@ class LayerStack:
                                                 C.c_int(N.qt(self.quant_type)), N.ptr(self._plan_mem[0]), C.c_size_t(nbytes),
                                                 C.byref(plan), N.stream()), "gemv_4bit_group_plan")
         self._ep_counter = torch.zeros(1, dtype=torch.int32, device=self.device)
-        self._tile_cnt = torch.zeros((cfg.hidden // g + 31) // 32, dtype=torch.int32, device=self.device)
+        # tagged exchange: accumulators and tile counts by layer parity (see the closer warp of the kernel)
+        self._tile_cnt = torch.zeros((2 if self._tagged else 1) * ((cfg.hidden // g + 31) // 32), dtype=torch.int32, device=self.device)
         ep = plan.ep
-        ep.acc, ep.alpha, ep.counter = self.acc.data_ptr(), self.alpha, self._ep_counter.data_ptr()
+        ep.acc, ep.alpha, ep.counter = (self.acc2 if self._tagged else self.acc).data_ptr(), self.alpha, self._ep_counter.data_ptr()
         ep.M, ep.hs, ep.H, ep.rank, ep.nranks = M, cfg.hidden // g, cfg.hidden, self.rank, g
         ep.peer_h, ep.nbuf, ep.peer_flags = self._peer_h_all.data_ptr(), self._nbuf, self._peer_flags.data_ptr()
         ep.step, ep.mul, ep.add = self.step_ctr.data_ptr(), L, 1

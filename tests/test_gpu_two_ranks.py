@@ -47,11 +47,11 @@ def _worker(rank, world, port, M, fused, boundary, persistent, tagged=None):
 @pytest.mark.parametrize("M,fused,boundary,persistent,tagged", [
     (1, True, "kernel", False, None), (4, True, "inline", False, None), (1, True, "stream", False, None),
     (8, True, "stream", False, None), (1, True, "stream", True, None), (5, True, "stream", True, None),
-    (1, True, "stream", True, False), (2, True, "stream", True, True),
+    (1, True, "stream", True, True), (2, True, "stream", True, True),
     (1, False, "kernel", False, None), (16, True, "kernel", False, None)])
 def test_two_rank_stack_matches_single_gpu(M, fused, boundary, persistent, tagged):
-    """fused: peer stores at the layer boundary (batch <= 8) - with flags, or (one launch per step, batch 1 unless forced)
-    as tagged entries; otherwise NCCL all-gather."""
+    """fused: peer stores at the layer boundary (batch <= 8) - with flags, or (one launch per step)
+    as tagged entries when asked for; otherwise NCCL all-gather."""
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     import torch.multiprocessing as mp
