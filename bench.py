@@ -1,7 +1,7 @@
 """Benchmark of the fused dequantise-matmul hot path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--batch M] [--model NAME]
-                    [--layers L] [--skip-extras] [--prefill-only] [--int8-only]
+                    [--layers L] [--skip-extras] [--prefill-only] [--int8-only] [--quant-only]
 
 Workload (every N): the Llama-70B-shaped NF4 decode stack of BASELINE config 5 - 80 layers x
 {q,o 8192x8192, k,v 1024x8192, gate/up 28672x8192, down 8192x28672}, double-quantised absmax,
@@ -26,7 +26,7 @@ line names it) and --skip-extras leaves out the further objects and the CPU base
 region of the main object is bracketed by cudaProfilerStart/Stop so that a profiler started with
 --profile-from-start off sees exactly the timed launches.
 
---prefill-only / --int8-only run just that object (used for profiler captures).
+--prefill-only / --int8-only / --quant-only run just that object (used for profiler captures).
 
 --impl reference times the reference's CPU algorithm (the C oracle: dequantise the whole
 weight, then matmul, as mps_bitsandbytes/functional.py:752-773 does on CPU) on one layer of
@@ -305,6 +305,75 @@ def int8_fp8_config4(torch, peaks, steps=10, warmup=3):
     return res
 
 
+def quantize_path(torch, peaks, steps=10, warmup=3):
+    """The memory-bound ends of the path on BASELINE config 5's largest weight (28672 x 8192 fp16): quantize_4bit
+    (NF4 / FP4, plain and double-quantised), dequantize_4bit, and the Embedding4bit / Embedding8bit gathers on a
+    128256 x 4096 table with 32768 indices.  GB/s are ALGORITHMIC bytes (16-bit side + packed + scales) over CUDA-event
+    time, against the measured HBM copy rate; inputs are larger than L2 and four input sets alternate.  Parity is
+    bit-exact by construction of the tests; here 64 sampled rows are compared byte for byte with the C oracle."""
+    import numpy as np
+    import mps_bitsandbytes_b200 as bnb
+    from oracle import oracle_c, oracle_np as O
+    n, k = 28672, 8192
+    g = torch.Generator(device="cuda"); g.manual_seed(5)
+    ws = [(torch.randn(n, k, device="cuda", generator=g) * 0.02).half() for _ in range(3)]
+    rows = np.sort(np.random.default_rng(5).choice(n, 64, replace=False))
+    peak = peaks["hbm_gbs"]
+    res = {"config": {"workload": f"weight {n}x{k} fp16, block 64; embeddings 128256x4096, 32768 indices",
+                      "l2": "470 MB per weight, three weights alternate: larger than L2"},
+           "unit": "GB/s", "peak": peak, "peak_source": peaks.get("source", "measured")}
+
+    def timed(fn, nbytes):
+        for i in range(warmup):
+            fn(i)
+        torch.cuda.synchronize()
+        ts = []
+        for i in range(steps):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(); fn(i); e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1))
+        ms = sorted(ts)[len(ts) // 2]
+        return {"ms": ms, "gbs": nbytes / ms / 1e6, "frac": nbytes / ms / 1e6 / peak, "bytes": nbytes}
+
+    nbytes = 2 * n * k + n * k // 2 + 4 * n * k // 64
+    for qt in ("nf4", "fp4"):
+        o = timed(lambda i: bnb.quantize_4bit(ws[i % 3], quant_type=qt), nbytes)
+        p, st = bnb.quantize_4bit(ws[0], quant_type=qt)
+        pc, ac = oracle_c.quantize_4bit(ws[0][torch.from_numpy(rows).cuda()].float().cpu().numpy(), 64, qt)
+        o["bit_exact"] = bool(np.array_equal(p.view(n, k // 2).cpu().numpy()[rows], pc.reshape(64, k // 2)) and
+                              np.array_equal(st.absmax.view(n, k // 64).cpu().numpy()[rows], ac.reshape(64, k // 64)))
+        res[f"quantize_4bit_{qt}"] = o
+        res[f"quantize_4bit_{qt}_double_quant"] = timed(
+            lambda i: bnb.quantize_4bit(ws[i % 3], quant_type=qt, compress_statistics=True), 2 * n * k + n * k // 2 + n * k // 64)
+    packs = [bnb.quantize_4bit(w, quant_type="nf4") for w in ws]
+    o = timed(lambda i: bnb.dequantize_4bit(*packs[i % 3]), nbytes)
+    d = bnb.dequantize_4bit(*packs[0])
+    dc = oracle_c.dequantize_4bit(packs[0][0].view(n, k // 2).cpu().numpy()[rows], packs[0][1].absmax.view(n, k // 64).cpu().numpy()[rows],
+                                  (64, k), 64, "nf4").astype(np.float16)
+    o["bit_exact"] = bool(np.array_equal(d.cpu().numpy()[rows], dc))
+    res["dequantize_4bit_nf4"] = o
+    del ws, packs, d
+    torch.cuda.empty_cache()
+    V, D, T = 128256, 4096, 32768
+    emb = torch.nn.Embedding(V, D, device="cuda", dtype=torch.float16)
+    ids = [torch.randint(0, V, (T,), device="cuda", generator=g) for _ in range(3)]
+    for name, mod, rd in (("embedding_4bit", bnb.Embedding4bit.from_embedding(emb), D // 2 + 4 * D // 64),
+                          ("embedding_8bit", bnb.Embedding8bit.from_embedding(emb), D + 4)):
+        o = timed(lambda i: mod(ids[i % 3]), T * (rd + 2 * D))
+        y = mod(ids[0][:64]).cpu().numpy()
+        i64 = ids[0][:64].cpu().numpy()
+        if name == "embedding_4bit":
+            sel = np.unique(i64)
+            # the oracle on the looked-up rows only
+            ref = O.embedding_4bit(np.searchsorted(sel, i64), mod.weight_packed.cpu().numpy()[sel], mod.weight_absmax.cpu().numpy()[sel], D)
+        else:
+            ref = O.embedding_8bit(i64, mod.weight_int8.cpu().numpy(), mod.weight_scales.cpu().numpy())
+        o["bit_exact"] = bool(np.array_equal(y, np.asarray(ref)))
+        res[name] = o
+    return res
+
+
 def oracle_stack_rows(ref_stack, x_rows):
     """The stack's dataflow (stack.py) on the CPU: every linear by the C oracle of the reference's CPU path
     (dequantise the whole weight to fp16, matmul with fp32 accumulation), on the given rows of x, from the packed
@@ -537,6 +606,10 @@ def run_gpu(args, cfg):
             out["int8_fp8"] = int8_fp8_config4(torch, peaks)
         except Exception as ex:
             out["int8_fp8"] = {"error": repr(ex)}
+        try:
+            out["quantize_path"] = quantize_path(torch, peaks)
+        except Exception as ex:
+            out["quantize_path"] = {"error": repr(ex)}
         out["cpu_baseline"] = cpu_baseline(cfg, M)
     if rank == 0:
         print(json.dumps(out), flush=True)
@@ -561,6 +634,7 @@ def main():
     ap.add_argument("--skip-extras", action="store_true", help="no prefill object, no CPU baseline")
     ap.add_argument("--prefill-only", action="store_true", help="only the prefill GEMM object (BASELINE config 2)")
     ap.add_argument("--int8-only", action="store_true", help="only the INT8 / FP8 / outlier-split object (BASELINE config 4)")
+    ap.add_argument("--quant-only", action="store_true", help="only the quantise / dequantise / embedding object")
     ap.add_argument("--exchange", default="fused", choices=["fused", "nccl"],
                     help="N > 1: layer boundary by peer stores + flags (default) or by an NCCL all-gather")
     ap.add_argument("--handoff", default="auto", choices=["auto", "tagged", "flags"],
@@ -579,6 +653,9 @@ def main():
     elif args.int8_only:
         import torch
         print(json.dumps(int8_fp8_config4(torch, load_peaks(), steps=args.steps, warmup=max(args.warmup, 3))))
+    elif args.quant_only:
+        import torch
+        print(json.dumps(quantize_path(torch, load_peaks(), steps=args.steps, warmup=max(args.warmup, 3))))
     elif args.impl == "reference":
         run_reference(args, cfg)
     else:

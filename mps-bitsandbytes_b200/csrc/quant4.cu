@@ -88,6 +88,66 @@ __device__ __forceinline__ uint32_t nf4_code_bucket(float v, const float2 *tab) 
     const uint32_t base = (uint32_t)(0xFEDCBA9764321100ull >> (4 * g)) & 15u;
     return base + (v > t.x ? 1u : 0u) + (v > t.y ? 1u : 0u);
 }
+// The search of the streaming quantiser, for quotients in [-1, 1] (|x| <= absmax of its own block): 32 buckets of width
+// 1/16, none of which holds more than one threshold; the bucket is the low six bits of fma_rz(v, 16, 2^23 + 16) =
+// floor(16 v + 16) - no conversion, no clamp (32, reached by v = 1 only, carries bucket 31's entry) - and
+// code = (thresholds below the bucket) + (v > the bucket's threshold, +inf if it has none).
+// oracle/oracle.c:o_prove_nf4_buckets32_rz compares it with the threshold search on every float of [-1, 1].
+// The table is replicated per lane - entry g of lane l at g * 256 + l * 8 bytes - so that a warp's 32 lookups are two
+// conflict-free wavefronts whatever the values are (the shared-memory pipe, not arithmetic, bounds this kernel).
+constexpr int NF4_B32_ENTRIES = 33;
+constexpr int NF4_B32_BYTES = NF4_B32_ENTRIES * 256;
+__device__ __forceinline__ void nf4_bucket32_fill(float2 *tab, int tid, int nthreads) {
+    const float t[15] = {NF4_T0, NF4_T1, NF4_T2, NF4_T3, NF4_T4, NF4_T5, NF4_T6, NF4_T7, NF4_T8, NF4_T9, NF4_T10, NF4_T11, NF4_T12, NF4_T13, NF4_T14};
+    for (int i = tid; i < NF4_B32_ENTRIES * 32; i += nthreads) {
+        const int g = i >> 5, b = g < 32 ? g : 31;
+        const float lo = -1.0f + (float)b * 0.0625f, hi = -1.0f + (float)(b + 1) * 0.0625f;   // exact
+        int below = 0;
+        float th = NF4_INF;
+#pragma unroll
+        for (int j = 0; j < 15; ++j) {
+            if (t[j] < lo) ++below;
+            else if (t[j] < hi) th = t[j];
+        }
+        tab[i] = make_float2(th, __int_as_float(below));
+    }
+}
+__device__ __forceinline__ uint32_t nf4_code_bucket32(float v, uint32_t tab_lane) {   // tab_lane: shared address of the table + lane * 8
+    const uint32_t bits = __float_as_uint(__fmaf_rz(v, 16.0f, 8388624.0f));
+    float th; uint32_t base;
+    asm("ld.shared.v2.b32 {%0, %1}, [%2];" : "=f"(th), "=r"(base) : "r"(tab_lane + ((bits & 63u) << 8)));
+    return base + (v > th ? 1u : 0u);
+}
+// FP4, same idea on the magnitude: 16 buckets of width 1/16 hold one of the seven thresholds at most; bucket = low five
+// bits of fma_rz(|v|, 16, 2^23) = floor(16 |v|) (16, reached by |v| = 1 only, carries bucket 15's entry); the sign as in
+// fp4_code.  oracle/oracle.c:o_prove_fp4_buckets16_rz checks every float of [-1, 1].  Entry g of lane l at g * 256 + l * 8.
+constexpr int FP4_B16_ENTRIES = 17;
+__device__ __forceinline__ void fp4_bucket16_fill(float2 *tab, int tid, int nthreads) {
+    const float t[7] = {FP4_T0, FP4_T1, FP4_T2, FP4_T3, FP4_T4, FP4_T5, FP4_T6};
+    for (int i = tid; i < FP4_B16_ENTRIES * 32; i += nthreads) {
+        const int g = i >> 5, b = g < 16 ? g : 15;
+        const float lo = (float)b * 0.0625f, hi = (float)(b + 1) * 0.0625f;   // exact
+        int below = 0;
+        float th = NF4_INF;
+#pragma unroll
+        for (int j = 0; j < 7; ++j) {
+            if (t[j] < lo) ++below;
+            else if (t[j] < hi) th = t[j];
+        }
+        tab[i] = make_float2(th, __int_as_float(below));
+    }
+}
+__device__ __forceinline__ uint32_t fp4_code_bucket16(float v, uint32_t tab_lane) {
+    const float a = fabsf(v);
+    const uint32_t bits = __float_as_uint(__fmaf_rz(a, 16.0f, 8388608.0f));
+    float th; uint32_t base;
+    asm("ld.shared.v2.b32 {%0, %1}, [%2];" : "=f"(th), "=r"(base) : "r"(tab_lane + ((bits & 31u) << 8)));
+    const uint32_t m = base + (a > th ? 1u : 0u);
+    return (v < 0.0f && m != 0u) ? (m | 8u) : m;                   // code 0 (+0.0) beats code 8 (-0.0) on the tie
+}
+template <int QT> __device__ __forceinline__ uint32_t code_unit(float v, uint32_t tab_lane) {
+    return QT == MPSBNB_NF4 ? nf4_code_bucket32(v, tab_lane) : fp4_code_bucket16(v, tab_lane);
+}
 template <int QT> __device__ __forceinline__ uint32_t code_fast(float v, const float2 *tab) {
     return QT == MPSBNB_NF4 ? nf4_code_bucket(v, tab) : fp4_code(v);
 }
@@ -185,6 +245,80 @@ quantize4_fast_kernel(const T *__restrict__ A, int64_t rows, int64_t cols, int64
             if (live) reinterpret_cast<uint32_t *>(packed)[cs[u]] = word;   // byte j/2: low nibble = even k
         }
     }
+}
+
+// ------------------------------------------------------------------------------------------
+// Streaming quantiser: the common case (16-bit input, block size 64, K a multiple of 64, maxima computed here).
+// The fast kernel above loads, computes and stores in turn, so its loads are in flight only part of the time
+// (measured 1.9 TB/s with exactly the algorithmic DRAM traffic: latency, not bytes or arithmetic).  Here every thread
+// keeps NS - 1 asynchronous 16-byte copies into its own slots of a shared-memory ring in flight WHILE it computes:
+// 80 bytes per thread, 120 KB per SM, whatever the arithmetic is doing.  A thread reads only what it copied
+// itself, so the copy groups' own completion is the only synchronisation.  With K a multiple of 64 the matrix is one
+// run of 8-element chunks: no row / column arithmetic, block = chunk / 8.
+// ------------------------------------------------------------------------------------------
+constexpr int QS_NS = 6;
+__device__ __forceinline__ void qs_cp_async16(void *dst_shared, const void *src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst_shared)), "l"(src) : "memory");
+}
+template <typename T, int QT>
+__global__ void __launch_bounds__(256, 6)
+quantize4_stream_kernel(const T *__restrict__ A, int64_t total, uint8_t *__restrict__ packed, float *__restrict__ absmax_out) {
+    static_assert(sizeof(T) == 2, "16-bit input");
+    __shared__ uint4 ring[QS_NS][256];
+    __shared__ __align__(16) float2 nf4_tab[(QT == MPSBNB_NF4 ? NF4_B32_ENTRIES : FP4_B16_ENTRIES) * 32];
+    const int tid = threadIdx.x, lane = tid & 31;
+    if (QT == MPSBNB_NF4) nf4_bucket32_fill(nf4_tab, tid, 256);
+    else fp4_bucket16_fill(nf4_tab, tid, 256);
+    __syncthreads();
+    const uint32_t tab_lane = (uint32_t)__cvta_generic_to_shared(nf4_tab) + (uint32_t)lane * 8u;
+    const int64_t stride = (int64_t)gridDim.x * 256;
+    int64_t c_next = (int64_t)blockIdx.x * 256 + tid;               // chunk of the next copy
+#pragma unroll
+    for (int s = 0; s < QS_NS - 1; ++s) {
+        if (c_next < total) qs_cp_async16(&ring[s][tid], A + c_next * 8);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        c_next += stride;
+    }
+    int slot = 0;
+    // total is a multiple of 8 and a warp's 32 chunks start at a multiple of 32: the eight lanes of a block are live
+    // together; the loop condition is warp-uniform (first lane's chunk) because of the shuffles
+    for (int64_t c = (int64_t)blockIdx.x * 256 + tid; c - lane < total; c += stride) {
+        asm volatile("cp.async.wait_group %0;" ::"n"(QS_NS - 2) : "memory");
+        const bool live = c < total;
+        uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+        if (live) raw = ring[slot][tid];
+        {   // refill the slot read one iteration ago (its values have been consumed)
+            const int ns = slot == 0 ? QS_NS - 1 : slot - 1;
+            if (c_next < total) qs_cp_async16(&ring[ns][tid], A + c_next * 8);
+            asm volatile("cp.async.commit_group;" ::: "memory");
+            c_next += stride;
+        }
+        slot = slot + 1 == QS_NS ? 0 : slot + 1;
+        float x[8];
+        {
+            const T *h = reinterpret_cast<const T *>(&raw);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) x[j] = to_f32<T>(h[j]);
+        }
+        float a = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) a = fmaxf(a, fabsf(x[j]));
+#pragma unroll
+        for (int o = 1; o < 8; o <<= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
+        a = fmaxf(a, 1e-8f);                                           // clamp(min=1e-8)
+        if (live && (lane & 7) == 0) absmax_out[c >> 3] = a;
+        uint32_t word = 0;
+        if (a > 1e-8f && a <= 1e30f) {                                 // a 16-bit input's magnitude: the shortcut is proven exact
+            const float r = __frcp_rn(a);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) word |= code_unit<QT>(block_div<true>(x[j], a, r), tab_lane) << (4 * j);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) word |= code_unit<QT>(block_div<false>(x[j], a, 0.f), tab_lane) << (4 * j);
+        }
+        if (live) reinterpret_cast<uint32_t *>(packed)[c] = word;      // byte j/2: low nibble = even k
+    }
+    asm volatile("cp.async.wait_all;" ::: "memory");
 }
 
 // ------------------------------------------------------------------------------------------
@@ -370,6 +504,19 @@ extern "C" int mpsbnb_quantize_4bit(const void *A, int a_dtype, int64_t rows, in
     const int64_t Kp = padded_k(cols, blocksize), nb = Kp / blocksize;
     const bool fast = is_16bit(a_dtype) && blocksize >= 32 && blocksize <= 256 && (cols % 8) == 0 &&
                       aligned16(A) && ((reinterpret_cast<uintptr_t>(packed) & 3) == 0);
+    if (fast && blocksize == 64 && cols % 64 == 0 && absmax_in == nullptr) {
+        const int64_t total = rows * (cols / 8);
+        const int64_t want = (total + 255) / 256;
+        const int grid = (int)(want < 6 * sm_count() ? want : 6 * sm_count());   // six CTAs per SM stay resident
+        if (quant_type == MPSBNB_NF4) {
+            if (a_dtype == MPSBNB_F16) quantize4_stream_kernel<__half, MPSBNB_NF4><<<grid, 256, 0, st>>>((const __half *)A, total, packed, absmax_out);
+            else quantize4_stream_kernel<__nv_bfloat16, MPSBNB_NF4><<<grid, 256, 0, st>>>((const __nv_bfloat16 *)A, total, packed, absmax_out);
+        } else {
+            if (a_dtype == MPSBNB_F16) quantize4_stream_kernel<__half, MPSBNB_FP4><<<grid, 256, 0, st>>>((const __half *)A, total, packed, absmax_out);
+            else quantize4_stream_kernel<__nv_bfloat16, MPSBNB_FP4><<<grid, 256, 0, st>>>((const __nv_bfloat16 *)A, total, packed, absmax_out);
+        }
+        return check_launch();
+    }
     if (fast) {
         const int64_t cpr = Kp / 8, total = rows * cpr;
         const int grid = grid_for((total + 31) / 32 * 32, 256, 16);

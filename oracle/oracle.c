@@ -14,6 +14,7 @@
  * Build: gcc -O2 -fopenmp -shared -fPIC -ffp-contract=off -o _build/liboracle.so oracle.c -lm
  * (-ffp-contract=off: no fused multiply-add may replace a rounded multiply and add.)
  */
+#include <fenv.h>
 #include <math.h>
 #include <omp.h>
 #include <stdint.h>
@@ -263,6 +264,113 @@ int64_t o_prove_nf4_buckets(int64_t stride) {
         g = g < 0 ? 0 : (g > 15 ? 15 : g);
         const int got = (int)((base >> (4 * g)) & 15u) + (v > ta[g]) + (v > tb[g]);
         bad += (got != o_nearest_by_threshold(v, 0, t));
+    }
+    return bad;
+}
+
+/* The NF4 search as the streaming CUDA quantiser does it: [-1, 1] in 32 buckets of width 1/16, none of which holds
+ * more than one of the fifteen thresholds; the bucket is the low six bits of fma_rz(v, 16, 2^23 + 16) =
+ * floor(16 v + 16) - no conversion, no clamp (32, reached by v = 1 only, uses bucket 31's entry) - and
+ * code = (thresholds below the bucket) + (v > the bucket's threshold).  Checked against the plain threshold search on
+ * every float of [-1, 1] whose ordered key is a multiple of `stride` (the quotient x / absmax of a block never leaves
+ * that interval); returns the number of disagreements (2^40 added if the rounding mode could not be set, 2^41 if a
+ * bucket holds two thresholds). */
+int64_t o_prove_nf4_buckets32_rz(int64_t stride) {
+    float t[15];
+    o_nf4_thresholds(t);
+    float tg[32];
+    int base[32];
+    int64_t bad = 0;
+    for (int g = 0; g < 32; ++g) {
+        const float lo = -1.0f + (float)g / 16.0f, hi = -1.0f + (float)(g + 1) / 16.0f;   /* exact */
+        int below = 0, inside = 0;
+        tg[g] = INFINITY;
+        for (int i = 0; i < 15; ++i) {
+            if (t[i] < lo) ++below;
+            else if (t[i] < hi) { tg[g] = t[i]; ++inside; }
+        }
+        base[g] = below;
+        if (inside > 1) bad += 1ll << 41;
+    }
+#pragma omp parallel reduction(+ : bad)
+    {
+        const int old_mode = fegetround();
+        fesetround(FE_TOWARDZERO);
+        {   /* the rounding mode must really be in force: a tiny negative v lands in bucket 15, not 16 */
+            volatile float tiny = -1e-30f;
+            const float f0 = fmaf(tiny, 16.0f, 8388624.0f);
+            uint32_t b0;
+            memcpy(&b0, &f0, 4);
+            if ((b0 & 63u) != 15u) bad += 1ll << 40;
+        }
+#pragma omp for schedule(static)
+        for (int64_t k = 0; k < 0x100000000ll; k += stride) {
+            const float v = unord((uint32_t)k);
+            if (isnan(v) || v < -1.0f || v > 1.0f) continue;
+            volatile float vv = v;                                   /* keeps the fma out of constant folding */
+            const float f = fmaf(vv, 16.0f, 8388624.0f);
+            uint32_t bits;
+            memcpy(&bits, &f, 4);
+            int g = (int)(bits & 63u);
+            if (g > 32) { bad += 1; continue; }
+            if (g == 32) g = 31;
+            const int got = base[g] + (v > tg[g]);
+            bad += (got != o_nearest_by_threshold(v, 0, t));
+        }
+        fesetround(old_mode);
+    }
+    return bad;
+}
+
+/* The FP4 search of the streaming CUDA quantiser: the magnitude a = |v| in 16 buckets of width 1/16, none of which
+ * holds more than one of the seven thresholds; bucket = low five bits of fma_rz(a, 16, 2^23) = floor(16 a) (16, reached
+ * by a = 1 only, uses bucket 15's entry); m = (thresholds below the bucket) + (a > the bucket's threshold); the sign
+ * as in the threshold form.  Every float of [-1, 1] whose ordered key is a multiple of `stride`. */
+int64_t o_prove_fp4_buckets16_rz(int64_t stride) {
+    float t[15];
+    o_fp4_thresholds(t);
+    float tg[16];
+    int base[16];
+    int64_t bad = 0;
+    for (int g = 0; g < 16; ++g) {
+        const float lo = (float)g / 16.0f, hi = (float)(g + 1) / 16.0f;   /* exact */
+        int below = 0, inside = 0;
+        tg[g] = INFINITY;
+        for (int i = 0; i < 7; ++i) {
+            if (t[i] < lo) ++below;
+            else if (t[i] < hi) { tg[g] = t[i]; ++inside; }
+        }
+        base[g] = below;
+        if (inside > 1) bad += 1ll << 41;
+    }
+#pragma omp parallel reduction(+ : bad)
+    {
+        const int old_mode = fegetround();
+        fesetround(FE_TOWARDZERO);
+        {   /* the rounding mode must really be in force: just below 1/16 stays in bucket 0 */
+            volatile float edge = 0.0624999963f;
+            const float f0 = fmaf(edge, 16.0f, 8388608.0f);
+            uint32_t b0;
+            memcpy(&b0, &f0, 4);
+            if ((b0 & 31u) != 0u) bad += 1ll << 40;
+        }
+#pragma omp for schedule(static)
+        for (int64_t k = 0; k < 0x100000000ll; k += stride) {
+            const float v = unord((uint32_t)k);
+            if (isnan(v) || v < -1.0f || v > 1.0f) continue;
+            volatile float aa = fabsf(v);
+            const float a = aa;
+            const float f = fmaf(aa, 16.0f, 8388608.0f);
+            uint32_t bits;
+            memcpy(&bits, &f, 4);
+            int g = (int)(bits & 31u);
+            if (g > 16) { bad += 1; continue; }
+            if (g == 16) g = 15;
+            const int m = base[g] + (a > tg[g]);
+            const int got = (v < 0.0f && m != 0) ? m + 8 : m;
+            bad += (got != o_nearest_by_threshold(v, 1, t));
+        }
+        fesetround(old_mode);
     }
     return bad;
 }

@@ -62,6 +62,23 @@ def test_nf4_bucket_search_equals_threshold_search():
     assert fn(C.c_int64(3)) == 0
 
 
+def test_nf4_bucket_search_by_truncating_fma_equals_threshold_search():
+    """The streaming quantiser's form (32 buckets of one threshold at most, bucket = low bits of
+    fma_rz(v, 16, 2^23 + 16), no conversion, no clamp) on every third float of [-1, 1], the range of x / absmax inside
+    a block (stride 1 also returns 0)."""
+    fn = oracle_c.lib().o_prove_nf4_buckets32_rz
+    fn.restype = C.c_int64
+    assert fn(C.c_int64(3)) == 0
+
+
+def test_fp4_bucket_search_by_truncating_fma_equals_threshold_search():
+    """FP4 form of the streaming quantiser (16 buckets over |v|, bucket = low bits of fma_rz(|v|, 16, 2^23)) on every
+    third float of [-1, 1] (stride 1 also returns 0)."""
+    fn = oracle_c.lib().o_prove_fp4_buckets16_rz
+    fn.restype = C.c_int64
+    assert fn(C.c_int64(3)) == 0
+
+
 @pytest.mark.parametrize("qt,bf16", [(0, 0), (1, 0), (0, 1), (1, 1)])
 def test_reciprocal_division_shortcut_is_exact_for_16bit_inputs(qt, bf16):
     """Every (x, absmax) pair of the format with absmax in the range where the kernel uses the
