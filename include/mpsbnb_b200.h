@@ -152,7 +152,8 @@ int mpsbnb_gemv_4bit_group_max_m(void);
  * are raised after the last tile.  Linears with an accumulator are scheduled first in a launch, so this
  * happens early and the exchange hides behind the rest of the launch.  Because h of the NEXT layer is
  * then written while THIS layer is still reading its own h, peer_h must not be the buffer the launch reads
- * x from (rotate three buffers when ranks may run more than a layer apart).
+ * x from (rotate three buffers when ranks may run more than a layer apart; when all segments run in ONE launch and
+ * some linears feed nothing that is waited for, give every segment its own buffer: a CTA may lag several segments).
  * Several segments in one launch (mpsbnb_linear4_desc.segment; streamed form only): the closing step of
  * segment g stores into buffer (g + 1) % nbuf — peer_h is then an array of nbuf * nranks pointers,
  * [buffer][rank] — and raises the flags to (*step) * mul + add + g; linears of segment g >= 1 wait

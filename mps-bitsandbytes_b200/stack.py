@@ -114,7 +114,8 @@ class LayerStack:
         self.fused_exchange = fused_exchange and world > 1
         # layer boundary (h' = alpha (o + down)) of the grouped path: "kernel" = its own small kernel after the GEMV
         # launch; "inline" = closing step of the GEMV launch (last CTA); "stream" = tile by tile inside the GEMV
-        # launch as soon as a tile's o and down contributions are complete (h rotates over three buffers)
+        # launch as soon as a tile's o and down contributions are complete (h rotates over three buffers, or has one
+        # per layer when the whole step is one launch)
         # Measured (7B step, one GPU): stream 1.167 ms, kernel 1.229 ms, inline 1.306 ms; across GPUs streaming also
         # hides the exchange.  With NCCL as the exchange the boundary has to be its own kernel.
         if boundary is None:
@@ -324,9 +325,10 @@ class LayerStack:
             self._plan_mem.append(mem)
 
     def _build_persistent_plan(self, M: int):
-        """One plan for the whole stack: 7 L linears, segment = layer.  Layer l reads h from buffer l % 3; the closing
-        step of segment l (streamed, by tiles) writes buffer (l + 1) % 3 on every rank and raises the flags to
-        step * L + l + 1; linears of layer l wait for flags >= step * L + l."""
+        """One plan for the whole stack: 7 L linears, segment = layer.  Layer l reads h from buffer l (one buffer per
+        layer plus the result); the closing step of segment l (streamed, by tiles) writes buffer l + 1 on every rank and
+        either adds to the per-rank counts of closed tiles - linears of layer l wait for counts >= (step L + l) T - or,
+        with the tagged exchange, writes entries that carry the tag step (L + 1) + l + 1, which layer l + 1 looks for."""
         cfg, lib, g, L = self.cfg, N.lib(), self.world, self.layers
         n = 7 * L
         if self._tagged:
