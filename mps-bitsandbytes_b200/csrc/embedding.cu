@@ -55,7 +55,7 @@ __global__ void __launch_bounds__(256) embedding4_vec_kernel(const void *__restr
         uint4 *dst = reinterpret_cast<uint4 *>(out + t * D + c * 16);
         const uint4 *src = reinterpret_cast<const uint4 *>(vals);
 #pragma unroll
-        for (int v = 0; v < (int)(sizeof(T) * 16 / 16); ++v) dst[v] = src[v];
+        for (int v = 0; v < (int)(sizeof(T) * 16 / 16); ++v) __stcs(dst + v, src[v]);
     }
 }
 
@@ -106,7 +106,7 @@ __global__ void __launch_bounds__(256) embedding8_kernel(const void *__restrict_
             uint4 *dst = reinterpret_cast<uint4 *>(out + t * D + c * 16);
             const uint4 *src = reinterpret_cast<const uint4 *>(vals);
 #pragma unroll
-            for (int v = 0; v < (int)(sizeof(T) * 16 / 16); ++v) dst[v] = src[v];
+            for (int v = 0; v < (int)(sizeof(T) * 16 / 16); ++v) __stcs(dst + v, src[v]);
         }
         return;
     }

@@ -448,7 +448,7 @@ dequantize4_stream_kernel(const uint8_t *__restrict__ packed, const void *__rest
             T *dst = out + i * 16;
 #pragma unroll
             for (int q = 0; q < (int)(sizeof(T) * 16 / 16); ++q)
-                reinterpret_cast<uint4 *>(dst)[q] = reinterpret_cast<const uint4 *>(vals)[q];
+                __stcs(reinterpret_cast<uint4 *>(dst) + q, reinterpret_cast<const uint4 *>(vals)[q]);   // written once, not re-read here
         }
     }
 }
