@@ -309,7 +309,8 @@ def quantize_path(torch, peaks, steps=10, warmup=3):
     """The memory-bound ends of the path on BASELINE config 5's largest weight (28672 x 8192 fp16): quantize_4bit
     (NF4 / FP4, plain and double-quantised), dequantize_4bit, and the Embedding4bit / Embedding8bit gathers on a
     128256 x 4096 table with 32768 indices.  GB/s are ALGORITHMIC bytes (16-bit side + packed + scales) over CUDA-event
-    time, against the measured HBM copy rate; inputs are larger than L2 and four input sets alternate.  Parity is
+    time of `steps` calls issued back to back, against the measured HBM copy rate (the median of single calls on an idle
+    GPU, which adds the host's time per call, is reported beside it); inputs are larger than L2 and three sets alternate.  Parity is
     bit-exact by construction of the tests; here 64 sampled rows are compared byte for byte with the C oracle."""
     import numpy as np
     import mps_bitsandbytes_b200 as bnb
@@ -328,13 +329,21 @@ def quantize_path(torch, peaks, steps=10, warmup=3):
             fn(i)
         torch.cuda.synchronize()
         ts = []
-        for i in range(steps):
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        for i in range(steps):                                      # one call at a time on an idle GPU: the host's
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)   # ~20 us per call show
             e0.record(); fn(i); e1.record()
             torch.cuda.synchronize()
             ts.append(e0.elapsed_time(e1))
-        ms = sorted(ts)[len(ts) // 2]
-        return {"ms": ms, "gbs": nbytes / ms / 1e6, "frac": nbytes / ms / 1e6 / peak, "bytes": nbytes}
+        single = sorted(ts)[len(ts) // 2]
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(steps):                                      # the same calls back to back (inputs still alternate)
+            fn(i)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / steps
+        return {"ms": ms, "gbs": nbytes / ms / 1e6, "frac": nbytes / ms / 1e6 / peak, "bytes": nbytes,
+                "ms_single_call_idle_gpu": single, "frac_single_call_idle_gpu": nbytes / single / 1e6 / peak}
 
     nbytes = 2 * n * k + n * k // 2 + 4 * n * k // 64
     for qt in ("nf4", "fp4"):
