@@ -511,6 +511,55 @@ quantize_blockwise_kernel(const T *__restrict__ A, int64_t n, int64_t bs, const 
     }
 }
 
+// Block size 256, fp32 input (the second level of double quantisation: one block maximum per 64 weights, millions of
+// them): a WARP per block - eight values per lane, maxima by shuffles, no CTA barrier - instead of a CTA per block with
+// three barriers each.  Same operations per element as above, so the same codes.
+__global__ void __launch_bounds__(256)
+quantize_blockwise256_f32_kernel(const float *__restrict__ A, int64_t n, const float *__restrict__ absmax_in,
+                                 int8_t *__restrict__ q, float *__restrict__ absmax_out) {
+    const int lane = threadIdx.x & 31;
+    const int64_t nblk = (n + 255) / 256;
+    const int64_t warp0 = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5), nwarps = (int64_t)gridDim.x * 8;
+    for (int64_t b = warp0; b < nblk; b += nwarps) {
+        const int64_t i0 = b * 256 + lane * 8;
+        float x[8];
+        if (i0 + 8 <= n) {
+            const float4 v0 = __ldg(reinterpret_cast<const float4 *>(A + i0)), v1 = __ldg(reinterpret_cast<const float4 *>(A + i0) + 1);
+            x[0] = v0.x; x[1] = v0.y; x[2] = v0.z; x[3] = v0.w; x[4] = v1.x; x[5] = v1.y; x[6] = v1.z; x[7] = v1.w;
+        } else {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) x[e] = i0 + e < n ? A[i0 + e] : 0.0f;
+        }
+        float a;
+        if (absmax_in != nullptr) {
+            a = absmax_in[b];
+        } else {
+            a = 0.0f;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) a = fmaxf(a, fabsf(x[e]));
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
+            a = fmaxf(a, 1e-8f);
+        }
+        if (lane == 0 && absmax_out != nullptr) absmax_out[b] = a;
+        const float scale = __fmul_rn(__frcp_rn(a), 127.0f);
+        uint32_t w[2] = {0u, 0u};
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            float v = rintf(__fmul_rn(x[e], scale));               // round half to even
+            v = fminf(fmaxf(v, -127.0f), 127.0f);
+            w[e >> 2] |= ((uint32_t)(int)v & 0xFFu) << (8 * (e & 3));
+        }
+        if (i0 + 8 <= n) {
+            *reinterpret_cast<uint2 *>(q + i0) = make_uint2(w[0], w[1]);
+        } else {
+#pragma unroll
+            for (int e = 0; e < 8; ++e)
+                if (i0 + e < n) q[i0 + e] = (int8_t)((w[e >> 2] >> (8 * (e & 3))) & 0xFFu);
+        }
+    }
+}
+
 template <typename T>
 __global__ void dequantize_blockwise_kernel(const int8_t *__restrict__ q, const float *__restrict__ absmax,
                                             int64_t n, int64_t bs, T *__restrict__ out) {
@@ -663,6 +712,13 @@ extern "C" int mpsbnb_quantize_blockwise(const void *A, int a_dtype, int64_t n, 
     if (n == 0) return MPSBNB_OK;
     if (A == nullptr || q == nullptr || (absmax_in == nullptr && absmax_out == nullptr)) return MPSBNB_ERR_INVALID_ARG;
     const int64_t nblk = (n + blocksize - 1) / blocksize;
+    if (blocksize == 256 && a_dtype == MPSBNB_F32 && aligned16(A) && (reinterpret_cast<uintptr_t>(q) & 7) == 0) {
+        int64_t g = (nblk + 7) / 8;
+        const int64_t gcap = (int64_t)sm_count() * 8;
+        if (g > gcap) g = gcap;
+        quantize_blockwise256_f32_kernel<<<(int)g, 256, 0, (cudaStream_t)stream>>>((const float *)A, n, absmax_in, q, absmax_out);
+        return check_launch();
+    }
     int64_t grid = nblk;
     const int64_t cap = (int64_t)sm_count() * 16;
     if (grid > cap) grid = cap;

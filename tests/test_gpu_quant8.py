@@ -32,6 +32,24 @@ def test_blockwise_golden_and_ties(golden):
     assert np.array_equal(to_np(bnb.dequantize_blockwise(q, st)), exp)
 
 
+@pytest.mark.parametrize("n", [256 * 5 + 37, 8, 256 * 1000, 255])
+def test_blockwise_256_fp32_ragged_and_ties_match_oracle(n):
+    """Block size 256 on fp32 input takes a warp-per-block kernel: whole blocks, a ragged last block, rounding ties
+    (values that are exact multiples of absmax / 254) and an all-zero block, byte for byte against the oracle."""
+    rng = np.random.default_rng(n)
+    x = (rng.standard_normal(n) * 0.05).astype(np.float32)
+    x[: min(n, 16)] = 0.0
+    if n > 300:
+        x[256:300] = np.float32(0.5) * np.arange(44, dtype=np.float32) / np.float32(127.0)   # .5 ties after scaling by 127 / 0.5...
+        x[300] = np.float32(0.5 * 43 / 127.0)
+    q, st = bnb.quantize_blockwise(torch.from_numpy(x).cuda(), blocksize=256)
+    eq, ea = O.quantize_blockwise(x, 256)
+    assert np.array_equal(to_np(q), eq) and np.array_equal(to_np(st.absmax), ea)
+    # a caller-given absmax takes the same kernel
+    q2, _ = bnb.quantize_blockwise(torch.from_numpy(x).cuda(), absmax=st.absmax.clone(), blocksize=256)
+    assert np.array_equal(to_np(q2), eq)
+
+
 def test_rowwise_golden_and_oracle(golden):
     g = golden("int8")
     q, s = bnb.quantize_rowwise(to_cuda(g["kat_row_in"], "float32"))
