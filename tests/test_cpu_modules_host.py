@@ -85,3 +85,46 @@ def test_new_entry_points_check_their_arguments():
     assert lib.mpsbnb_outlier_linear(*args(2, 0, None, 4096)) == -1
     assert lib.mpsbnb_outlier_linear(*args(0, 3, one, 4096)) == -1
     assert lib.mpsbnb_outlier_linear(*args(0, 0, None, 100)) == -4
+
+
+def test_short_argument_tensors_are_refused_before_any_kernel(monkeypatch):
+    """The kernels take raw pointers, so every wrapper compares the lengths of caller-supplied tensors with the shapes
+    before it launches (the reference raises a shape error in the same places).  Run on CPU tensors with the device
+    check switched off and a library stub that fails the test if any entry point is reached."""
+    from mps_bitsandbytes_b200 import functional as F
+
+    class NoLaunch:
+        def __getattr__(self, name):
+            raise AssertionError(f"{name} reached with a short argument")
+
+    monkeypatch.setattr(F, "_check_device", lambda *a, **k: None)
+    monkeypatch.setattr(N, "require_cuda", lambda *a, **k: None, raising=False)
+    monkeypatch.setattr(N, "lib", lambda: NoLaunch())
+    K, n = 200, 64                                                  # rows padded to 256 in the packed layout
+    packed = torch.zeros(n * 128, dtype=torch.uint8)
+    st = bnb.QuantState(absmax=torch.ones(n * 4), shape=torch.Size((n, K)), blocksize=64, quant_type="nf4", dtype=torch.float16)
+    x = torch.zeros(3, K, dtype=torch.float16)
+    with pytest.raises(ValueError, match="packed weight"):
+        bnb.matmul_4bit(x, packed[:-8], st)
+    with pytest.raises(ValueError, match="bias"):
+        bnb.matmul_4bit(x, packed, st, torch.zeros(n - 1, dtype=torch.float16))
+    short = bnb.QuantState(absmax=st.absmax[:-1], shape=st.shape, blocksize=64, quant_type="nf4", dtype=st.dtype)
+    with pytest.raises(ValueError, match="absmax"):
+        bnb.matmul_4bit(x, packed, short)
+    q = torch.zeros(8, 32, dtype=torch.int8)
+    with pytest.raises(ValueError, match="scales"):
+        bnb.dequantize_rowwise(q, torch.ones(7))
+    with pytest.raises(ValueError, match="scales"):
+        bnb.dequantize_fp8_e4m3(q.view(torch.uint8), torch.ones(7))
+    with pytest.raises(ValueError, match="col_scales"):
+        bnb.dequantize_colrow(q, torch.ones(8), torch.ones(31))
+    with pytest.raises(ValueError, match="B_scales"):
+        bnb.matmul_int8(q, torch.zeros(32, 16, dtype=torch.int8), torch.ones(8), torch.ones(15))
+    with pytest.raises(ValueError, match="weight_row_scales"):
+        bnb.matmul_colrow(torch.zeros(2, 32, dtype=torch.float16), q, torch.ones(7), torch.ones(32))
+    with pytest.raises(ValueError, match="weight_scales"):
+        bnb.matmul_fp8_e4m3(torch.zeros(2, 32, dtype=torch.float16), q.view(torch.uint8), torch.ones(7))
+    with pytest.raises(ValueError, match="row_stats"):
+        bnb.double_quant(torch.zeros(8, 32), row_stats=torch.ones(7))
+    with pytest.raises(ValueError, match="absmax"):
+        bnb.quantize_blockwise(torch.zeros(1000), absmax=torch.ones(1), blocksize=256)
