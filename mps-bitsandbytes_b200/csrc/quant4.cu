@@ -115,7 +115,8 @@ __device__ __forceinline__ void nf4_bucket32_fill(float2 *tab, int tid, int nthr
 __device__ __forceinline__ uint32_t nf4_code_bucket32(float v, uint32_t tab_lane) {   // tab_lane: shared address of the table + lane * 8
     const uint32_t bits = __float_as_uint(__fmaf_rz(v, 16.0f, 8388624.0f));
     float th; uint32_t base;
-    asm("ld.shared.v2.b32 {%0, %1}, [%2];" : "=f"(th), "=r"(base) : "r"(tab_lane + ((bits & 63u) << 8)));
+    // bits = 0x4B000000 + bucket: shifted left by 8 the constant part leaves the 32-bit word, so no mask is needed
+    asm("ld.shared.v2.b32 {%0, %1}, [%2];" : "=f"(th), "=r"(base) : "r"(tab_lane + (bits << 8)));
     return base + (v > th ? 1u : 0u);
 }
 // FP4, same idea on the magnitude: 16 buckets of width 1/16 hold one of the seven thresholds at most; bucket = low five
@@ -141,7 +142,7 @@ __device__ __forceinline__ uint32_t fp4_code_bucket16(float v, uint32_t tab_lane
     const float a = fabsf(v);
     const uint32_t bits = __float_as_uint(__fmaf_rz(a, 16.0f, 8388608.0f));
     float th; uint32_t base;
-    asm("ld.shared.v2.b32 {%0, %1}, [%2];" : "=f"(th), "=r"(base) : "r"(tab_lane + ((bits & 31u) << 8)));
+    asm("ld.shared.v2.b32 {%0, %1}, [%2];" : "=f"(th), "=r"(base) : "r"(tab_lane + (bits << 8)));   // (as for NF4: no mask)
     const uint32_t m = base + (a > th ? 1u : 0u);
     return (v < 0.0f && m != 0u) ? (m | 8u) : m;                   // code 0 (+0.0) beats code 8 (-0.0) on the tie
 }
@@ -311,10 +312,10 @@ quantize4_stream_kernel(const T *__restrict__ A, int64_t total, uint8_t *__restr
         if (a > 1e-8f && a <= 1e30f) {                                 // a 16-bit input's magnitude: the shortcut is proven exact
             const float r = __frcp_rn(a);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) word |= code_unit<QT>(block_div<true>(x[j], a, r), tab_lane) << (4 * j);
+            for (int j = 0; j < 8; ++j) word += code_unit<QT>(block_div<true>(x[j], a, r), tab_lane) << (4 * j);   // nibbles do not overlap: + is |
         } else {
 #pragma unroll
-            for (int j = 0; j < 8; ++j) word |= code_unit<QT>(block_div<false>(x[j], a, 0.f), tab_lane) << (4 * j);
+            for (int j = 0; j < 8; ++j) word += code_unit<QT>(block_div<false>(x[j], a, 0.f), tab_lane) << (4 * j);
         }
         if (live) reinterpret_cast<uint32_t *>(packed)[c] = word;      // byte j/2: low nibble = even k
     }

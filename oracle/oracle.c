@@ -311,6 +311,7 @@ int64_t o_prove_nf4_buckets32_rz(int64_t stride) {
             const float f = fmaf(vv, 16.0f, 8388624.0f);
             uint32_t bits;
             memcpy(&bits, &f, 4);
+            if ((bits & 0xFFFFFFC0u) != 0x4B000000u) { bad += 1; continue; }   /* the kernel adds bits << 8 to the table address unmasked */
             int g = (int)(bits & 63u);
             if (g > 32) { bad += 1; continue; }
             if (g == 32) g = 31;
@@ -363,6 +364,7 @@ int64_t o_prove_fp4_buckets16_rz(int64_t stride) {
             const float f = fmaf(aa, 16.0f, 8388608.0f);
             uint32_t bits;
             memcpy(&bits, &f, 4);
+            if ((bits & 0xFFFFFFE0u) != 0x4B000000u) { bad += 1; continue; }   /* bits << 8 is used unmasked */
             int g = (int)(bits & 31u);
             if (g > 16) { bad += 1; continue; }
             if (g == 16) g = 15;
