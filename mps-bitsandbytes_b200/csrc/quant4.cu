@@ -261,9 +261,9 @@ constexpr int QS_NS = 6;
 __device__ __forceinline__ void qs_cp_async16(void *dst_shared, const void *src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst_shared)), "l"(src) : "memory");
 }
-template <typename T, int QT>
+template <typename T, int QT, typename IDX>                        // IDX: chunk counters in 32 bits where the matrix allows it
 __global__ void __launch_bounds__(256, 6)
-quantize4_stream_kernel(const T *__restrict__ A, int64_t total, uint8_t *__restrict__ packed, float *__restrict__ absmax_out) {
+quantize4_stream_kernel(const T *__restrict__ A, IDX total, uint8_t *__restrict__ packed, float *__restrict__ absmax_out) {
     static_assert(sizeof(T) == 2, "16-bit input");
     __shared__ uint4 ring[QS_NS][256];
     __shared__ __align__(16) float2 nf4_tab[(QT == MPSBNB_NF4 ? NF4_B32_ENTRIES : FP4_B16_ENTRIES) * 32];
@@ -272,52 +272,56 @@ quantize4_stream_kernel(const T *__restrict__ A, int64_t total, uint8_t *__restr
     else fp4_bucket16_fill(nf4_tab, tid, 256);
     __syncthreads();
     const uint32_t tab_lane = (uint32_t)__cvta_generic_to_shared(nf4_tab) + (uint32_t)lane * 8u;
-    const int64_t stride = (int64_t)gridDim.x * 256;
-    int64_t c_next = (int64_t)blockIdx.x * 256 + tid;               // chunk of the next copy
+    const IDX stride = (IDX)gridDim.x * 256;
+    IDX c_next = (IDX)blockIdx.x * 256 + (IDX)tid;                   // chunk of the next copy
 #pragma unroll
     for (int s = 0; s < QS_NS - 1; ++s) {
-        if (c_next < total) qs_cp_async16(&ring[s][tid], A + c_next * 8);
+        if (c_next < total) qs_cp_async16(&ring[s][tid], A + (size_t)c_next * 8);
         asm volatile("cp.async.commit_group;" ::: "memory");
         c_next += stride;
     }
-    int slot = 0;
     // total is a multiple of 8 and a warp's 32 chunks start at a multiple of 32: the eight lanes of a block are live
-    // together; the loop condition is warp-uniform (first lane's chunk) because of the shuffles
-    for (int64_t c = (int64_t)blockIdx.x * 256 + tid; c - lane < total; c += stride) {
-        asm volatile("cp.async.wait_group %0;" ::"n"(QS_NS - 2) : "memory");
-        const bool live = c < total;
-        uint4 raw = make_uint4(0u, 0u, 0u, 0u);
-        if (live) raw = ring[slot][tid];
-        {   // refill the slot read one iteration ago (its values have been consumed)
-            const int ns = slot == 0 ? QS_NS - 1 : slot - 1;
-            if (c_next < total) qs_cp_async16(&ring[ns][tid], A + c_next * 8);
+    // together; the loop condition is warp-uniform (first lane's chunk) because of the shuffles.  The ring's slots are
+    // taken in turn by an unrolled inner loop, so slot numbers are constants.
+    IDX c = (IDX)blockIdx.x * 256 + (IDX)tid;
+    bool more = true;
+    while (more) {
+#pragma unroll
+        for (int s = 0; s < QS_NS; ++s) {
+            if (c - (IDX)lane >= total) { more = false; break; }
+            asm volatile("cp.async.wait_group %0;" ::"n"(QS_NS - 2) : "memory");
+            const bool live = c < total;
+            uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+            if (live) raw = ring[s][tid];
+            // refill the slot read one iteration ago (its values have been consumed)
+            if (c_next < total) qs_cp_async16(&ring[(s + QS_NS - 1) % QS_NS][tid], A + (size_t)c_next * 8);
             asm volatile("cp.async.commit_group;" ::: "memory");
             c_next += stride;
+            float x[8];
+            {
+                const T *h = reinterpret_cast<const T *>(&raw);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) x[j] = to_f32<T>(h[j]);
+            }
+            float a = 0.0f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) a = fmaxf(a, fabsf(x[j]));
+#pragma unroll
+            for (int o = 1; o < 8; o <<= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
+            a = fmaxf(a, 1e-8f);                                       // clamp(min=1e-8)
+            if (live && (lane & 7) == 0) absmax_out[(size_t)(c >> 3)] = a;
+            uint32_t word = 0;
+            if (a > 1e-8f && a <= 1e30f) {                             // a 16-bit input's magnitude: the shortcut is proven exact
+                const float r = __frcp_rn(a);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) word += code_unit<QT>(block_div<true>(x[j], a, r), tab_lane) << (4 * j);   // nibbles do not overlap: + is |
+            } else {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) word += code_unit<QT>(block_div<false>(x[j], a, 0.f), tab_lane) << (4 * j);
+            }
+            if (live) reinterpret_cast<uint32_t *>(packed)[(size_t)c] = word;   // byte j/2: low nibble = even k
+            c += stride;
         }
-        slot = slot + 1 == QS_NS ? 0 : slot + 1;
-        float x[8];
-        {
-            const T *h = reinterpret_cast<const T *>(&raw);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) x[j] = to_f32<T>(h[j]);
-        }
-        float a = 0.0f;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) a = fmaxf(a, fabsf(x[j]));
-#pragma unroll
-        for (int o = 1; o < 8; o <<= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
-        a = fmaxf(a, 1e-8f);                                           // clamp(min=1e-8)
-        if (live && (lane & 7) == 0) absmax_out[c >> 3] = a;
-        uint32_t word = 0;
-        if (a > 1e-8f && a <= 1e30f) {                                 // a 16-bit input's magnitude: the shortcut is proven exact
-            const float r = __frcp_rn(a);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) word += code_unit<QT>(block_div<true>(x[j], a, r), tab_lane) << (4 * j);   // nibbles do not overlap: + is |
-        } else {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) word += code_unit<QT>(block_div<false>(x[j], a, 0.f), tab_lane) << (4 * j);
-        }
-        if (live) reinterpret_cast<uint32_t *>(packed)[c] = word;      // byte j/2: low nibble = even k
     }
     asm volatile("cp.async.wait_all;" ::: "memory");
 }
@@ -602,13 +606,21 @@ extern "C" int mpsbnb_quantize_4bit(const void *A, int a_dtype, int64_t rows, in
         const int64_t total = rows * (cols / 8);
         const int64_t want = (total + 255) / 256;
         const int grid = (int)(want < 6 * sm_count() ? want : 6 * sm_count());   // six CTAs per SM stay resident
+#define LAUNCH_STREAM(T, QT)                                                                                             \
+    do {                                                                                                                 \
+        if (total < 0x7f000000ll)                                                                                        \
+            quantize4_stream_kernel<T, QT, uint32_t><<<grid, 256, 0, st>>>((const T *)A, (uint32_t)total, packed, absmax_out); \
+        else                                                                                                             \
+            quantize4_stream_kernel<T, QT, int64_t><<<grid, 256, 0, st>>>((const T *)A, total, packed, absmax_out);      \
+    } while (0)
         if (quant_type == MPSBNB_NF4) {
-            if (a_dtype == MPSBNB_F16) quantize4_stream_kernel<__half, MPSBNB_NF4><<<grid, 256, 0, st>>>((const __half *)A, total, packed, absmax_out);
-            else quantize4_stream_kernel<__nv_bfloat16, MPSBNB_NF4><<<grid, 256, 0, st>>>((const __nv_bfloat16 *)A, total, packed, absmax_out);
+            if (a_dtype == MPSBNB_F16) LAUNCH_STREAM(__half, MPSBNB_NF4);
+            else LAUNCH_STREAM(__nv_bfloat16, MPSBNB_NF4);
         } else {
-            if (a_dtype == MPSBNB_F16) quantize4_stream_kernel<__half, MPSBNB_FP4><<<grid, 256, 0, st>>>((const __half *)A, total, packed, absmax_out);
-            else quantize4_stream_kernel<__nv_bfloat16, MPSBNB_FP4><<<grid, 256, 0, st>>>((const __nv_bfloat16 *)A, total, packed, absmax_out);
+            if (a_dtype == MPSBNB_F16) LAUNCH_STREAM(__half, MPSBNB_FP4);
+            else LAUNCH_STREAM(__nv_bfloat16, MPSBNB_FP4);
         }
+#undef LAUNCH_STREAM
         return check_launch();
     }
     if (fast) {
